@@ -8,4 +8,4 @@ timeout -k 10 900 $TR bench.py --gpus 2 --steps 3 --warmup 3 --no-e2e --profile 
 head -12 gpurun_out/prof_n2_c.txt | cut -c1-150
 CUDA_VISIBLE_DEVICES=0 timeout -k 10 900 python bench.py --steps 3 --warmup 3 --no-e2e --profile gpurun_out/prof_n1_c.txt > gpurun_out/b1_c.log 2>&1; echo "bench1 rc=$?"; grep -a '"metric"' gpurun_out/b1_c.log | cut -c1-500
 head -14 gpurun_out/prof_n1_c.txt | cut -c1-150
-CUDA_VISIBLE_DEVICES=0 timeout -k 10 600 ncu --set full --clock-control none --import-source on -k regex:gemm_tcgen05_2cta -s 4 -c 1 -f -o gpurun_out/gemm_2cta python tests/bench_gemm.py > gpurun_out/ncu_gemm2.log 2>&1; echo "ncu rc=$?"
+CUDA_VISIBLE_DEVICES=0 timeout -k 10 600 ncu --set full --clock-control none -k regex:gemm_tcgen05_2cta -s 4 -c 1 -f -o gpurun_out/gemm_2cta python tests/bench_gemm.py > gpurun_out/ncu_gemm2.log 2>&1; echo "ncu rc=$?"

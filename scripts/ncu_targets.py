@@ -1,5 +1,5 @@
 """Tiny drivers for `ncu` captures: each target launches ONE kernel family a few times on representative shapes.
-    ncu --set full --clock-control none --import-source on -k regex:<kernel> -s 2 -c 1 -o gpurun_out/ncu_<t> python scripts/ncu_targets.py <t>
+    ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 1 -o gpurun_out/ncu_<t> python scripts/ncu_targets.py <t>
 """
 import os
 import sys

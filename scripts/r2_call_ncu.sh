@@ -3,7 +3,7 @@
 # contraction kernels is kept; every capture is also exported as raw / details CSV on the box (small text files).
 mkdir -p gpurun_out; export PYTHONPATH=$PWD:$PYTHONPATH
 cap() { name=$1; regex=$2; tgt=$3; keep=$4
-  timeout 240 ncu --set full --clock-control none --import-source on -k regex:$regex -s 2 -c 1 -f -o gpurun_out/ncu_$name python scripts/ncu_targets.py $tgt > gpurun_out/ncu_$name.log 2>&1; echo "$name rc=$?"
+  timeout 240 ncu --set full --clock-control none -k regex:$regex -s 2 -c 1 -f -o gpurun_out/ncu_$name python scripts/ncu_targets.py $tgt > gpurun_out/ncu_$name.log 2>&1; echo "$name rc=$?"
   if [ -f gpurun_out/ncu_$name.ncu-rep ]; then
     ncu -i gpurun_out/ncu_$name.ncu-rep --page raw --csv > gpurun_out/ncu_${name}_raw.csv 2>/dev/null
     ncu -i gpurun_out/ncu_$name.ncu-rep --page details --csv > gpurun_out/ncu_${name}_details.csv 2>/dev/null
