@@ -44,6 +44,10 @@ class KVCacheManager:
         self.max_blocks_per_sequence = (self.max_input_length + self.max_output_length + self.block_size - 1) \
             // self.block_size
         self.num_blocks = self.max_blocks_per_sequence * self.max_batch_size * self.beam_width
+        if getattr(config, "max_cache_tokens", None):
+            # the pool is sized for the tokens that are live at once, not for every sequence at full length
+            self.num_blocks = (config.max_cache_tokens + self.block_size - 1) // self.block_size
+        self.model_config = model_config
         self._kv_caches = self._init_device_caches()
         self._cache_blocks: Tuple[CacheBlock, ...] = self._init_logical_caches()
         self._available_blocks = self.num_blocks
@@ -64,6 +68,8 @@ class KVCacheManager:
 
     @property
     def total_physical_cache_size_in_bytes(self) -> int:
+        if getattr(self, "_kv_caches", None) and self._kv_caches[0] is not None:
+            return sum(t.numel() * t.element_size() for side in self._kv_caches for t in side if t is not None)
         return (2 * self.num_layers * self.num_blocks * self.block_size * self.kv_head_num * self.head_size
                 * self.elem_size_in_bytes)
 
@@ -192,6 +198,16 @@ class KVCacheManager:
         return tuple(CacheBlock(i, self.block_size, self.elem_size_in_bytes) for i in range(self.num_blocks))
 
     def _init_device_caches(self):
+        if getattr(self.model_config, "layer_specs", None) is not None:
+            # hybrid decoders: only attention layers hold pages, and K and V heads may differ in width
+            from .state_cache import layer_cache_shapes
+
+            k, v = [], []
+            for i in range(self.num_layers):
+                shp = layer_cache_shapes(self.model_config, i, self.num_blocks, self.block_size, self.tp_size)
+                k.append(None if shp is None else torch.zeros(shp[0], dtype=self.kv_cache_dtype, device=self.device))
+                v.append(None if shp is None else torch.zeros(shp[1], dtype=self.kv_cache_dtype, device=self.device))
+            return k, v
         shape = (self.num_blocks, self.block_size, self.kv_head_num, self.head_size)
         k = [torch.zeros(shape, dtype=self.kv_cache_dtype, device=self.device) for _ in range(self.num_layers)]
         v = [torch.zeros(shape, dtype=self.kv_cache_dtype, device=self.device) for _ in range(self.num_layers)]

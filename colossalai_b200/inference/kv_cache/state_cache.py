@@ -1,0 +1,79 @@
+"""Fixed-size recurrent state per live sequence, beside the paged K / V of attention layers.
+
+A recurrent mixer (linear attention, delta rule) keeps, per sequence, an fp32 matrix per head and - where it has short
+convolutions - the last few inputs of every convolved channel.  The pool holds `max_batch_size` slots per such layer; a
+sequence takes a slot when it is admitted and gives it back when it ends.  Slots are not cleared: the kernels take the
+state of a sequence that has consumed no token yet as zero.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ...accelerator import get_accelerator
+
+__all__ = ["StateCacheManager", "layer_cache_shapes", "layer_state_shapes"]
+
+
+def _spec(model_config, layer: int):
+    specs = getattr(model_config, "layer_specs", None)
+    return None if specs is None else specs[layer].mixer
+
+
+def layer_cache_shapes(model_config, layer: int, num_blocks: int, block_size: int,
+                       tp_size: int = 1) -> Optional[Tuple[Tuple[int, ...], Tuple[int, ...]]]:
+    """(K shape, V shape) of a layer's paged cache, None for a layer without one."""
+    sp = _spec(model_config, layer)
+    if sp is None:
+        kv = max(getattr(model_config, "num_key_value_heads", model_config.num_attention_heads) // tp_size, 1)
+        shp = (num_blocks, block_size, kv, model_config.head_dim)
+        return shp, shp
+    if sp.kind != "attention":
+        return None
+    return (num_blocks, block_size, sp.kv_heads, sp.dim), (num_blocks, block_size, sp.kv_heads, sp.vdim)
+
+
+def layer_state_shapes(model_config, layer: int, slots: int) -> Optional[Dict[str, Tuple[int, ...]]]:
+    """Shapes of a recurrent layer's state tensors ("S": fp32 memory, "conv": carried convolution inputs)."""
+    sp = _spec(model_config, layer)
+    if sp is None or not sp.recurrent:
+        return None
+    out = {"S": (slots, sp.heads, sp.dim, sp.vdim)}
+    if sp.conv > 1:
+        out["conv"] = (slots, sp.conv - 1, 2 * sp.kv_heads * sp.dim + sp.heads * sp.vdim)
+    return out
+
+
+class StateCacheManager:
+    def __init__(self, config, model_config) -> None:
+        self.device = get_accelerator().get_current_device()
+        self.num_slots = config.max_batch_size
+        self.dtype = config.dtype
+        self._free: List[int] = list(range(self.num_slots))
+        self.states: List[Optional[Dict[str, torch.Tensor]]] = []
+        for i in range(model_config.num_hidden_layers):
+            shapes = layer_state_shapes(model_config, i, self.num_slots)
+            self.states.append(None if shapes is None else {
+                n: torch.zeros(s, dtype=torch.float32 if n == "S" else self.dtype, device=self.device)
+                for n, s in shapes.items()})
+
+    @property
+    def num_available_slots(self) -> int:
+        return len(self._free)
+
+    @property
+    def has_state(self) -> bool:
+        return any(s is not None for s in self.states)
+
+    def allocate(self) -> int:
+        if not self._free:
+            raise RuntimeError("No state slot available.")
+        return self._free.pop(0)
+
+    def free(self, slot: int) -> None:
+        assert 0 <= slot < self.num_slots and slot not in self._free
+        self._free.append(slot)
+
+    def total_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for s in self.states if s is not None for t in s.values())

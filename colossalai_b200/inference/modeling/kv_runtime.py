@@ -18,9 +18,13 @@ __all__ = ["PagedKVRuntime"]
 
 
 class PagedKVRuntime:
-    def __init__(self, k_caches: List[torch.Tensor], v_caches: List[torch.Tensor], block_size: int) -> None:
+    def __init__(self, k_caches: List[torch.Tensor], v_caches: List[torch.Tensor], block_size: int,
+                 states: Optional[List[Optional[dict]]] = None) -> None:
         self.k_caches, self.v_caches = k_caches, v_caches
         self.block_size = block_size
+        self.states = states                                  # per layer: recurrent state tensors indexed by slot
+        self.ragged = None                                    # ops.mixers.RaggedMeta of the step (ragged steps)
+        self.shared: dict = {}                                # tensors one layer lends to later ones within a step
         self.block_tables: Optional[torch.Tensor] = None      # [bsz, max_blocks] int32 (device)
         self.seq_lens: Optional[torch.Tensor] = None          # [bsz] int32, INCLUDING the tokens of this step
         self.is_prompt = True
@@ -54,6 +58,56 @@ class PagedKVRuntime:
         self.token_seq = seq.to(device=device, dtype=torch.int32)
         self.token_pos = pos.to(device=device, dtype=torch.int32)
         return pos.to(device=device, dtype=torch.int64)
+
+    # ------------------------------------------------------------------ ragged steps (portions + decoded tokens)
+    def set_ragged_step(self, block_tables: torch.Tensor, q_lens, ctx_lens, slots, device) -> torch.Tensor:
+        """A step in which sequence i brings `q_lens[i]` new tokens on top of `ctx_lens[i]` cached ones: whole prompts,
+        portions of prompts and single decoded tokens side by side.  Returns the int64 position of every token."""
+        from ...ops.mixers import RaggedMeta
+
+        self.ragged = RaggedMeta.build(q_lens, ctx_lens, slots, device)
+        self.block_tables = block_tables.to(device=device, dtype=torch.int32).contiguous()
+        self.token_seq, self.token_pos = self.ragged.token_seq, self.ragged.token_pos
+        self.seq_lens = self.ragged.ctx_len + (self.ragged.cu_q[1:] - self.ragged.cu_q[:-1])
+        self.is_prompt, self.q_per_seq, self.cu_seqlens = False, 1, None
+        self.max_len_host = max((c + n for c, n in zip(self.ragged.ctx_lens, self.ragged.q_lens)), default=0)
+        self.shared = {}
+        return self.token_pos.long()
+
+    def layer_state(self, layer_idx: int) -> dict:
+        return self.states[layer_idx]
+
+    def attend_ragged(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+                      bias_table=None, bucket_starts=None, sink: bool = False, v_other=None,
+                      lam: float = 0.0) -> torch.Tensor:
+        """Write the step's K / V rows (values optionally blended with `v_other`) into the layer's pages, then attend
+        every step token over positions 0..pos of its sequence.  q [T, H x dim], k [T, G x dim], v [T, G x vdim]."""
+        from ...ops import mixers as mops
+
+        kc, vc = self.k_caches[layer_idx], self.v_caches[layer_idx]
+        mops.paged_kv_write_mix(k, v, kc, vc, self.block_tables, self.ragged, v_other=v_other, lam=lam)
+        return mops.paged_bias_attention(q, kc, vc, self.block_tables, self.ragged, scale, bias_table=bias_table,
+                                         bucket_starts=bucket_starts, sink=sink)
+
+    @classmethod
+    def scratch(cls, cfg, batch: int, seqlen: int, device, dtype, block_size: int = 16) -> "PagedKVRuntime":
+        """Cache pages and state slots for `batch` fresh sequences of `seqlen` tokens, laid out back to back: what a
+        forward without a serving engine runs on."""
+        from ..kv_cache.state_cache import layer_cache_shapes, layer_state_shapes
+
+        per = (seqlen + block_size - 1) // block_size
+        ks, vs, states = [], [], []
+        for i in range(cfg.num_hidden_layers):
+            shp = layer_cache_shapes(cfg, i, batch * per, block_size)
+            ks.append(None if shp is None else torch.zeros(shp[0], dtype=dtype, device=device))
+            vs.append(None if shp is None else torch.zeros(shp[1], dtype=dtype, device=device))
+            st = layer_state_shapes(cfg, i, batch)
+            states.append(None if st is None else {
+                n: torch.zeros(sh, dtype=torch.float32 if n == "S" else dtype, device=device) for n, sh in st.items()})
+        rt = cls(ks, vs, block_size, states)
+        tables = torch.arange(batch * per, dtype=torch.int32).view(batch, per)
+        rt.set_ragged_step(tables, [seqlen] * batch, [0] * batch, list(range(batch)), device)
+        return rt
 
     def attend(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta, scale: float,
                alibi_slopes: Optional[torch.Tensor] = None, sliding_window: Optional[int] = None) -> torch.Tensor:

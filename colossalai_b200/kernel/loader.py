@@ -50,6 +50,8 @@ LIBS: Dict[str, dict] = {
     "cb200_moe": {"sources": ["moe.cu"], "kind": "cuda"},
     "cb200_infer": {"sources": ["inference.cu"], "kind": "cuda"},
     "cb200_quant": {"sources": ["quant.cu"], "kind": "cuda"},
+    # recurrences and softmax in IEEE fp32 (no approximate exp / division): built without --use_fast_math
+    "cb200_mixers": {"sources": ["mixers.cu"], "kind": "cuda", "drop_flags": ["--use_fast_math"]},
     "cb200_cpu_adam": {"sources": ["cpu_adam.cpp"], "kind": "cpp"},
     "cb200_aio": {"sources": ["async_file_io.cpp"], "kind": "cpp", "extra": ["-lpthread"]},
 }
@@ -90,8 +92,13 @@ def _src_hash(name: str) -> str:
         h.update((CSRC / s).read_bytes())
     for hdr in sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")):
         h.update(hdr.read_bytes())
-    h.update(" ".join(NVCC_FLAGS if spec["kind"] == "cuda" else CXX_FLAGS).encode())
+    h.update(" ".join(_flags(spec)).encode())
     return h.hexdigest()[:16]
+
+
+def _flags(spec: dict) -> List[str]:
+    base = NVCC_FLAGS if spec["kind"] == "cuda" else CXX_FLAGS
+    return [f for f in base if f not in spec.get("drop_flags", ())]
 
 
 def lib_path(name: str) -> Path:
@@ -119,12 +126,12 @@ def build(name: str, verbose: bool = False, force: bool = False) -> Path:
         nvcc = _nvcc()
         if nvcc is None:
             raise RuntimeError("nvcc not found; cannot build CUDA kernels")
-        cmd = [nvcc] + NVCC_FLAGS + ["-I", str(CSRC)] + (["-Xptxas", "-v"] if verbose else []) + srcs + \
+        cmd = [nvcc] + _flags(spec) + ["-I", str(CSRC)] + (["-Xptxas", "-v"] if verbose else []) + srcs + \
               ["-o", str(out), "-lcuda"] + spec.get("extra", [])
         # libcuda may be absent on the build box: resolve driver entry points at run time instead
         cmd = [c for c in cmd if c != "-lcuda"]
     else:
-        cmd = ["g++"] + CXX_FLAGS + ["-I", str(CSRC)] + srcs + ["-o", str(out)] + spec.get("extra", [])
+        cmd = ["g++"] + _flags(spec) + ["-I", str(CSRC)] + srcs + ["-o", str(out)] + spec.get("extra", [])
     tmp = str(out) + f".tmp{os.getpid()}"
     cmd[cmd.index(str(out))] = tmp
     res = subprocess.run(cmd, capture_output=True, text=True)

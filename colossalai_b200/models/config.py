@@ -8,7 +8,7 @@ from __future__ import annotations
 from dataclasses import asdict, dataclass, field, replace
 from typing import Any, Dict, List, Optional
 
-__all__ = ["ModelConfig", "MoEConfig", "MODEL_ZOO", "get_config"]
+__all__ = ["ModelConfig", "MoEConfig", "MixerSpec", "LayerSpec", "MODEL_ZOO", "get_config"]
 
 
 @dataclass
@@ -27,6 +27,58 @@ class MoEConfig:
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
     capacity_factor: float = 0.0                  # 0 = dropless
+
+
+@dataclass
+class MixerSpec:
+    """The token mixer of one layer of a hybrid decoder (`ModelConfig.layer_specs`).
+
+    kind "attention":  softmax attention over a paged cache; q/k heads `dim` wide, value heads `vdim` wide; optional
+                       learned bias per (distance bucket, head) with `bias_buckets` rows (first half exact distances,
+                       second half logarithmic up to `bias_max`), optional zero-score `sink` in the softmax denominator,
+                       optional RMS norm over the whole q / k projection, optional blend of the values with those of the
+                       first `v_mix` layer.
+    kind "lightning":  per-head outer-product memory with one scalar `decay` per head, read out by q.
+    kind "channel_delta": gated delta rule with a decay per head and key channel, short causal convolutions of `conv`
+                       taps on q, k, v, low-rank (`decay_rank`, `gate_rank`) projections for the decay and output gate."""
+
+    kind: str = "attention"
+    heads: int = 1
+    kv_heads: Optional[int] = None
+    dim: int = 64
+    vdim: Optional[int] = None
+    bias: bool = False
+    scale: Optional[float] = None
+    bias_buckets: int = 0
+    bias_max: float = 0.0
+    sink: bool = False
+    proj_norm: bool = False
+    v_mix: bool = False
+    decay: Optional[List[float]] = None
+    conv: int = 0
+    decay_rank: int = 0
+    gate_rank: int = 0
+
+    def __post_init__(self) -> None:
+        if self.kv_heads is None:
+            self.kv_heads = self.heads
+        if self.vdim is None:
+            self.vdim = self.dim
+        assert self.heads % self.kv_heads == 0, "query heads must be a multiple of key/value heads"
+
+    @property
+    def recurrent(self) -> bool:
+        return self.kind != "attention"
+
+
+@dataclass
+class LayerSpec:
+    mixer: MixerSpec = field(default_factory=MixerSpec)
+    ff: Optional[int] = None          # feed-forward width; None = the layer has no feed-forward
+
+    def __post_init__(self) -> None:
+        if isinstance(self.mixer, dict):
+            self.mixer = MixerSpec(**self.mixer)
 
 
 @dataclass
@@ -75,11 +127,22 @@ class ModelConfig:
     qk_nope_head_dim: int = 0
     qk_rope_head_dim: int = 0
     v_head_dim: int = 0
+    # hybrid decoders: one spec per layer (mixer kind and sizes, feed-forward width) instead of the uniform fields above
+    layer_specs: Optional[List[LayerSpec]] = None
+    norm_placement: str = "pre"       # "pre": sublayer(norm(x)); "sublayer_out": x + residual_mult * norm(sublayer(x))
+    residual_mult: float = 1.0
+    norm_weight_offset: float = 0.0   # weights stored around zero: the norm multiplies by (offset + w)
+    fp32_residual: bool = False       # the residual stream stays in fp32 whatever the compute dtype
     pad_token_id: Optional[int] = None
     bos_token_id: int = 1
     eos_token_id: int = 2
 
     def __post_init__(self) -> None:
+        if self.layer_specs is not None:
+            self.layer_specs = [LayerSpec(**s) if isinstance(s, dict) else s for s in self.layer_specs]
+            self.num_hidden_layers = len(self.layer_specs)
+            att = [s.mixer for s in self.layer_specs if s.mixer.kind == "attention"] or [self.layer_specs[0].mixer]
+            self.num_attention_heads, self.num_key_value_heads, self.head_dim = att[0].heads, att[0].kv_heads, att[0].dim
         if self.num_key_value_heads is None:
             self.num_key_value_heads = self.num_attention_heads
         if self.kv_lora_rank is not None:

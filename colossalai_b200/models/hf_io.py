@@ -29,6 +29,10 @@ _LLAMA_LIKE = ("llama", "mistral", "qwen2", "qwen3", "mixtral", "baichuan", "com
 
 def config_from_hf(hf: dict) -> ModelConfig:
     mt = hf.get("model_type", "llama")
+    if hf.get("architecture") == "Gopunex":
+        from .gopunex import gopunex_config
+
+        return gopunex_config(hf)
     if mt == "gpt2":
         return ModelConfig(model_type="gpt2", vocab_size=hf["vocab_size"], hidden_size=hf["n_embd"],
                            intermediate_size=hf.get("n_inner") or 4 * hf["n_embd"], num_hidden_layers=hf["n_layer"],
@@ -471,7 +475,12 @@ def load_hf_checkpoint(path: str, dtype: torch.dtype = torch.bfloat16, device: s
     from . import build_model
 
     with open(os.path.join(path, "config.json")) as f:
-        cfg = config_from_hf(json.load(f))
+        hf_cfg = json.load(f)
+    if hf_cfg.get("architecture") == "Gopunex":
+        from .gopunex import load_gopunex
+
+        return load_gopunex(path, hf_cfg, dtype, device)
+    cfg = config_from_hf(hf_cfg)
     model = build_model(cfg).to(dtype)
     merged: Dict[str, torch.Tensor] = {}
     for shard in iter_hf_shards(path):

@@ -1,0 +1,150 @@
+"""Token mixers of hybrid decoders, beside the rotary / ALiBi `Attention` of `transformer.py`:
+
+  * `BiasSinkAttention`: softmax attention over the paged cache with a learned bias per (distance bucket, head), a
+    zero-score sink in the denominator, an RMS norm over the whole q / k projection and a blend of the values with
+    those of the first value-mixing layer;
+  * `LightningAttention`: linear attention with one scalar decay per head (an outer-product memory per head);
+  * `ChannelDeltaMixer`: gated delta rule with a decay per head and key channel and short causal convolutions.
+
+Every mixer keeps the call signature of `Attention` (`forward(x, meta, rope, kv_cache)`) and is selected per layer by
+`ModelConfig.layer_specs[i].mixer.kind` (`build_mixer`).  `kv_cache` is the step runtime (`inference.modeling.PagedKVRuntime`):
+it carries the ragged layout of the step, the paged K / V of attention layers and the per-slot recurrent state of the
+others, so a whole prompt, a portion of one and a single decoded token all take the same path.  Sizes and constants come
+from the `MixerSpec`; what the design fixes (activation choices, where the unit norm sits) is in the code.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..ops import mixers as mops
+from .config import MixerSpec, ModelConfig
+
+__all__ = ["BiasSinkAttention", "LightningAttention", "ChannelDeltaMixer", "build_mixer"]
+
+
+class _MixerBase(nn.Module):
+    def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
+        super().__init__()
+        self.cfg, self.spec, self.layer_idx = cfg, spec, layer_idx
+        self.shard_config = None
+        self._aux_cache: Dict[Tuple[str, str], torch.Tensor] = {}
+
+    def _aux(self, name: str, device, make) -> torch.Tensor:
+        """Small constant tensors in exact fp32 / int32 on the compute device (built once per device)."""
+        key = (name, str(device))
+        if key not in self._aux_cache:
+            self._aux_cache[key] = make().to(device)
+        return self._aux_cache[key]
+
+    def _apply(self, fn, *a, **k):          # parameters moved or cast: the derived constants are rebuilt
+        self._aux_cache = {}
+        return super()._apply(fn, *a, **k)
+
+
+class BiasSinkAttention(_MixerBase):
+    def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
+        super().__init__(cfg, spec, layer_idx)
+        H, G, d, dv = spec.heads, spec.kv_heads, spec.dim, spec.vdim
+        self.qkv_proj = nn.Linear(cfg.hidden_size, H * d + G * d + G * dv, bias=spec.bias)
+        if spec.proj_norm:
+            self.q_norm_weight = nn.Parameter(torch.ones(H * d))
+            self.k_norm_weight = nn.Parameter(torch.ones(G * d))
+        if spec.bias_buckets:
+            self.rel_bias = nn.Parameter(torch.zeros(spec.bias_buckets, H))
+        if spec.v_mix:
+            self.v_mix = nn.Parameter(torch.zeros(()))
+        self.o_proj = nn.Linear(H * dv, cfg.hidden_size, bias=False)
+        self.scale = spec.scale if spec.scale is not None else d ** -0.5
+
+    def forward(self, x: torch.Tensor, meta, rope=None, kv_cache=None) -> torch.Tensor:
+        sp, eps = self.spec, self.cfg.norm_eps
+        H, G, d, dv = sp.heads, sp.kv_heads, sp.dim, sp.vdim
+        qkv = self.qkv_proj(x)
+        q, k, v = qkv.split([H * d, G * d, G * dv], dim=-1)
+        if sp.proj_norm:
+            q = ops.rms_norm(q.contiguous(), self.q_norm_weight, eps)
+            k = ops.rms_norm(k.contiguous(), self.k_norm_weight, eps)
+        v_other, lam = None, 0.0
+        if sp.v_mix:
+            first = kv_cache.shared.get("v_first")
+            if first is None:
+                kv_cache.shared["v_first"] = v          # the first value-mixing layer lends its values, unblended
+            else:
+                v_other = first
+                lam = self._aux("lam", "cpu", lambda: self.v_mix.detach().float().cpu()).item()
+        table = starts = None
+        if sp.bias_buckets:
+            table = self._aux("rel", x.device, lambda: self.rel_bias.detach().float().contiguous())
+            starts = self._aux("starts", x.device, lambda: torch.tensor(
+                mops.log_bucket_starts(sp.bias_buckets, sp.bias_max), dtype=torch.int32))
+        o = kv_cache.attend_ragged(self.layer_idx, q, k, v, self.scale, bias_table=table, bucket_starts=starts,
+                                   sink=sp.sink, v_other=v_other, lam=lam)
+        return self.o_proj(o)
+
+
+class LightningAttention(_MixerBase):
+    def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
+        super().__init__(cfg, spec, layer_idx)
+        H, d, dv = spec.heads, spec.dim, spec.vdim
+        assert spec.decay is not None and len(spec.decay) == H, "one decay per head"
+        self.in_proj = nn.Linear(cfg.hidden_size, 2 * H * d + 2 * H * dv, bias=False)      # q | k | v | gate
+        self.norm_weight = nn.Parameter(torch.ones(H * dv))
+        self.o_proj = nn.Linear(H * dv, cfg.hidden_size, bias=False)
+
+    def forward(self, x: torch.Tensor, meta, rope=None, kv_cache=None) -> torch.Tensor:
+        sp = self.spec
+        H, d, dv = sp.heads, sp.dim, sp.vdim
+        z = self.in_proj(x)
+        q, k, v, g = z.split([H * d, H * d, H * dv, H * dv], dim=-1)
+        decay = self._aux("decay", x.device, lambda: torch.tensor(sp.decay, dtype=torch.float64).float())
+        st = kv_cache.layer_state(self.layer_idx)
+        o = mops.state_scan_decay(q, k, v, decay, st["S"], kv_cache.ragged, H, d, dv, act_silu=True)
+        o = mops.gated_group_rms_norm(o, self.norm_weight, g, H * dv, self.cfg.norm_eps, x.dtype)
+        return self.o_proj(o)
+
+
+class ChannelDeltaMixer(_MixerBase):
+    def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
+        super().__init__(cfg, spec, layer_idx)
+        H, G, d, dv = spec.heads, spec.kv_heads, spec.dim, spec.vdim
+        self.conv_channels = 2 * G * d + H * dv
+        # q | k | v | write strength | decay bottleneck | gate bottleneck: one GEMM reads the layer input
+        self.in_proj = nn.Linear(cfg.hidden_size, self.conv_channels + H + spec.decay_rank + spec.gate_rank, bias=False)
+        self.conv_weight = nn.Parameter(torch.zeros(self.conv_channels, max(spec.conv, 1)))
+        self.decay_up = nn.Linear(spec.decay_rank, H * d, bias=False)
+        self.gate_up = nn.Linear(spec.gate_rank, H * dv, bias=False)
+        self.A_log = nn.Parameter(torch.zeros(H))
+        self.dt_bias = nn.Parameter(torch.zeros(H * d))
+        self.norm_weight = nn.Parameter(torch.ones(dv))
+        self.o_proj = nn.Linear(H * dv, cfg.hidden_size, bias=False)
+
+    def forward(self, x: torch.Tensor, meta, rope=None, kv_cache=None) -> torch.Tensor:
+        sp = self.spec
+        H, G, d, dv = sp.heads, sp.kv_heads, sp.dim, sp.vdim
+        z = self.in_proj(x)
+        qkv, b, a1, g1 = z.split([self.conv_channels, H, sp.decay_rank, sp.gate_rank], dim=-1)
+        st = kv_cache.layer_state(self.layer_idx)
+        ragged = kv_cache.ragged
+        qkv = mops.short_conv_silu(qkv, self.conv_weight, st["conv"], ragged)
+        q, k, v = qkv.split([G * d, G * d, H * dv], dim=-1)
+        a = self.decay_up(a1)
+        gate = self.gate_up(g1)
+        a_log = self._aux("A_log", x.device, lambda: self.A_log.detach().float())
+        dt_bias = self._aux("dt_bias", x.device, lambda: self.dt_bias.detach().float())
+        o = mops.state_scan_delta(q, k, v, a, b, a_log, dt_bias, st["S"], ragged, H, G, d, dv)
+        o = mops.gated_group_rms_norm(o, self.norm_weight, gate, dv, self.cfg.norm_eps, x.dtype)
+        return self.o_proj(o)
+
+
+_KINDS = {"attention": BiasSinkAttention, "lightning": LightningAttention, "channel_delta": ChannelDeltaMixer}
+
+
+def build_mixer(cfg: ModelConfig, layer_idx: int) -> nn.Module:
+    spec = cfg.layer_specs[layer_idx].mixer
+    if spec.kind not in _KINDS:
+        raise ValueError(f"unknown mixer kind {spec.kind!r}; known: {sorted(_KINDS)}")
+    return _KINDS[spec.kind](cfg, spec, layer_idx)

@@ -51,6 +51,8 @@ class SeqMeta:
     max_seqlen: Optional[int] = None
     attn_mask: Optional[torch.Tensor] = None   # [B, S] padding mask (1 = keep) for encoder models
     local_seqlen: Optional[int] = None          # per-sequence tokens held by this rank under a2a / ring_attn
+    stream_cast: Optional[torch.Tensor] = None  # compute-dtype copy of an fp32 residual stream (written by the fused
+                                                # norm + residual kernel, read by the next sublayer's GEMM)
 
 
 def _use_fused_a2a(x: torch.Tensor, sp_group) -> bool:
@@ -67,7 +69,9 @@ def _use_fused_a2a(x: torch.Tensor, sp_group) -> bool:
 def build_norm(cfg: ModelConfig, hidden: Optional[int] = None) -> nn.Module:
     h = hidden or cfg.hidden_size
     if cfg.norm_type == "rms":
-        return FusedRMSNorm(h, eps=cfg.norm_eps)
+        norm = FusedRMSNorm(h, eps=cfg.norm_eps, offset=cfg.norm_weight_offset)
+        norm.reset_parameters()
+        return norm
     return FusedLayerNorm(h, eps=cfg.norm_eps)
 
 
@@ -331,11 +335,19 @@ class DecoderLayer(nn.Module):
         super().__init__()
         self.cfg, self.layer_idx = cfg, layer_idx
         self.input_layernorm = build_norm(cfg)
-        self.self_attn = MLAttention(cfg, layer_idx) if cfg.use_mla else Attention(cfg, layer_idx)
-        if not cfg.parallel_block:
+        spec = cfg.layer_specs[layer_idx] if cfg.layer_specs is not None else None
+        if spec is not None:
+            from .mixers import build_mixer
+
+            self.self_attn = build_mixer(cfg, layer_idx)
+        else:
+            self.self_attn = MLAttention(cfg, layer_idx) if cfg.use_mla else Attention(cfg, layer_idx)
+        if not cfg.parallel_block and (spec is None or spec.ff is not None):
             self.post_attention_layernorm = build_norm(cfg)
         moe = cfg.moe
-        if moe is not None and layer_idx >= moe.first_k_dense_replace and (layer_idx % moe.moe_layer_freq == 0):
+        if spec is not None:
+            self.mlp = MLP(cfg, spec.ff) if spec.ff is not None else None
+        elif moe is not None and layer_idx >= moe.first_k_dense_replace and (layer_idx % moe.moe_layer_freq == 0):
             from .moe import SparseMoE
 
             self.mlp = SparseMoE(cfg)
@@ -345,6 +357,8 @@ class DecoderLayer(nn.Module):
 
     def forward(self, x: torch.Tensor, meta: SeqMeta, rope=None, kv_cache=None) -> torch.Tensor:
         cfg = self.cfg
+        if cfg.norm_placement == "sublayer_out":
+            return self._forward_sublayer_out(x, meta, rope, kv_cache)
         if cfg.post_norm:   # BERT: x = LN(x + attn(x)); x = LN(x + mlp(x))
             x = self.input_layernorm(x + self.self_attn(x, meta, rope, kv_cache))
             return self.post_attention_layernorm(x + self.mlp(x))
@@ -359,6 +373,29 @@ class DecoderLayer(nn.Module):
             x = x + a
             h = self.post_attention_layernorm(x)
         return x + self.mlp(h)
+
+
+    def _forward_sublayer_out(self, x: torch.Tensor, meta: SeqMeta, rope, kv_cache) -> torch.Tensor:
+        """x <- x + m * norm(mixer(x)); x <- x + m * norm(ff(x)): the sublayers read the stream itself and only their
+        output is normalised.  With an fp32 stream one kernel normalises, scales, adds and writes the compute-dtype copy
+        the next GEMM reads (`meta.stream_cast`)."""
+        cfg = self.cfg
+        dt = self.input_layernorm.weight.dtype
+        fp32_stream = x.dtype == torch.float32 and cfg.fp32_residual
+        if not fp32_stream:
+            x = x.float()
+        h = meta.stream_cast if (fp32_stream and meta.stream_cast is not None) else x.to(dt)
+        y = self.self_attn(h, meta, rope, kv_cache)
+        h = ops.rms_norm_residual(x, y, self.input_layernorm.weight, cfg.norm_eps, cfg.residual_mult,
+                                  cfg.norm_weight_offset)
+        if self.mlp is not None:
+            y = self.mlp(h)
+            h = ops.rms_norm_residual(x, y, self.post_attention_layernorm.weight, cfg.norm_eps, cfg.residual_mult,
+                                      cfg.norm_weight_offset)
+        if fp32_stream:
+            meta.stream_cast = h
+            return x
+        return h
 
 
 class TransformerModel(nn.Module):
@@ -429,6 +466,8 @@ class TransformerModel(nn.Module):
               inputs_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
         cfg = self.cfg
         x = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+        if cfg.fp32_residual:
+            x = x.float()
         if cfg.embed_scale != 1.0:
             x = x * cfg.embed_scale
         if cfg.pos_type == "learned":
@@ -522,6 +561,12 @@ class TransformerModel(nn.Module):
         else:
             x = hidden_states
         rope = self.rope_cache(device, min_len=int(getattr(meta, "seqlen", 0) or 0))
+        if cfg.layer_specs is not None and kv_cache is None:
+            # a plain forward of a hybrid decoder is a prefill of B fresh sequences into a scratch cache and state pool
+            from ..inference.modeling.kv_runtime import PagedKVRuntime
+
+            kv_cache = PagedKVRuntime.scratch(cfg, B, S, device, self.norm.weight.dtype if cfg.final_norm
+                                              else self.embed_tokens.weight.dtype)
         start, end = self.layer_range()
         n_ckpt = self._num_ckpt_layers(end - start) if self.training else 0
         for i in range(start, end):
@@ -531,7 +576,10 @@ class TransformerModel(nn.Module):
             else:
                 x = layer(x, meta, rope, kv_cache)
         if last and cfg.final_norm:
-            x = self.norm(x)
+            if cfg.fp32_residual and x.dtype == torch.float32:
+                x = ops.rms_norm_f32in(x, self.norm.weight, cfg.norm_eps, cfg.norm_weight_offset)
+            else:
+                x = self.norm(x)
         return x
 
 
@@ -576,7 +624,9 @@ class TransformerLMHeadModel(nn.Module):
                 hidden_states: Optional[torch.Tensor] = None, token_type_ids: Optional[torch.Tensor] = None,
                 batch: Optional[int] = None, seqlen: Optional[int] = None, return_logits: bool = True,
                 kv_cache=None, meta=None, inputs_embeds: Optional[torch.Tensor] = None,
-                **unused) -> Dict[str, torch.Tensor]:
+                logit_positions: Optional[torch.Tensor] = None, **unused) -> Dict[str, torch.Tensor]:
+        """`logit_positions` (flat token indices): only those rows go through the LM head (serving: the last token of a
+        prompt portion, or the positions a caller asked for)."""
         cfg, sc = self.cfg, self.shard_config
         sm = sc.pipeline_stage_manager if sc is not None else None
         if input_ids is not None:
@@ -599,6 +649,8 @@ class TransformerLMHeadModel(nn.Module):
         if sp_mode in ("all_to_all", "ring_attn") and not keep_sp_sharded and comm.group_size(sp_group) > 1:
             Sl = h.shape[0] // B
             h = gather_sp_output(h.view(B, Sl, -1), sp_group, sp_mode, sp_dim=1).reshape(B * S, -1)
+        if logit_positions is not None:
+            h = h.index_select(0, logit_positions)
         if cfg.norm_head:
             # Baichuan-2 NormHead: L2-normalised rows.  Rows are vocabulary entries, so the normalisation is local to
             # a vocab-parallel shard too; run the (possibly parallel) head with the normalised weight swapped in.

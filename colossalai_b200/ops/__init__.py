@@ -3,6 +3,7 @@ from ._dispatch import force_torch, is_forced_torch, use_native
 from .activation import bias_act, get_activation, glu, glu_ref, swiglu
 from .attention import attention, attention_ref, attention_with_lse_ref
 from .gemm import linear_forward, matmul_nn, matmul_tn
+from .mixers import rms_norm_f32in, rms_norm_residual
 from .norm import layer_norm, layer_norm_ref, rms_norm, rms_norm_ref
 from .rope import build_rope_cache, rope_qkv, rope_ref
 

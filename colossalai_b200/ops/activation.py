@@ -136,6 +136,8 @@ def get_activation(name: str):
         return F.gelu
     if name == "relu":
         return F.relu
+    if name in ("relu2", "relu_squared"):
+        return lambda x: F.relu(x).square()
     if name == "quick_gelu":
         return lambda x: x * torch.sigmoid(1.702 * x)
     raise ValueError(f"unknown activation {name}")

@@ -1,0 +1,349 @@
+"""Python face of the sequence-mixer kernels (kernel/csrc/mixers.cu): short causal convolution with a carried window,
+recurrent state scans (decayed outer-product state, gated delta rule), group RMS norm with a sigmoid gate, RMS norm of a
+sublayer's output added to an fp32 residual stream, and paged attention with a distance-bucket bias and a softmax sink.
+
+All ops take a RAGGED step (`RaggedMeta`): for every live sequence its next tokens, how many tokens earlier steps
+consumed, and the slot that holds its carried state.  CUDA tensors go to the sm_100a kernels; CPU tensors take the plain
+PyTorch path below (the plumbing tier of the test-suite), which follows the same token-by-token order.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+from ..kernel import loader
+from ._dispatch import use_native
+from ._dtypes import code
+
+__all__ = ["RaggedMeta", "short_conv_silu", "state_scan_decay", "state_scan_delta", "gated_group_rms_norm",
+           "rms_norm_residual", "rms_norm_f32in", "paged_kv_write_mix", "paged_bias_attention", "log_bucket_starts"]
+
+_lib = None
+
+
+def _get_lib():
+    global _lib
+    if _lib is None:
+        _lib = loader.load("cb200_mixers")
+    return _lib
+
+
+def _i64(v: int) -> ctypes.c_int64:
+    return ctypes.c_int64(int(v))
+
+
+def _f(v: float) -> ctypes.c_float:
+    return ctypes.c_float(float(v))
+
+
+@dataclass
+class RaggedMeta:
+    """One step's layout.  Device tensors are int32; the python lists mirror them so no op has to synchronise."""
+
+    cu_q: torch.Tensor            # [nseq + 1] first flat token of every sequence's portion
+    ctx_len: torch.Tensor         # [nseq] tokens consumed by earlier steps
+    slots: torch.Tensor           # [nseq] state slot of the sequence
+    token_seq: torch.Tensor       # [T] sequence index of every token
+    token_pos: torch.Tensor       # [T] position of every token in its sequence
+    q_lens: List[int]
+    ctx_lens: List[int]
+    slot_list: List[int]
+
+    @property
+    def nseq(self) -> int:
+        return len(self.q_lens)
+
+    @property
+    def max_q(self) -> int:
+        return max(self.q_lens) if self.q_lens else 0
+
+    @staticmethod
+    def build(q_lens: Sequence[int], ctx_lens: Sequence[int], slots: Sequence[int], device) -> "RaggedMeta":
+        q_lens, ctx_lens, slots = [int(x) for x in q_lens], [int(x) for x in ctx_lens], [int(x) for x in slots]
+        cu = [0]
+        seq, pos = [], []
+        for i, (n, c) in enumerate(zip(q_lens, ctx_lens)):
+            cu.append(cu[-1] + n)
+            seq += [i] * n
+            pos += range(c, c + n)
+        flat = torch.tensor(cu + ctx_lens + slots + seq + pos, dtype=torch.int32).to(device, non_blocking=True)
+        n = len(q_lens)
+        a, b, c, d = n + 1, 2 * n + 1, 3 * n + 1, 3 * n + 1 + len(seq)
+        return RaggedMeta(flat[:a], flat[a:b], flat[b:c], flat[c:d], flat[d:], q_lens, ctx_lens, slots)
+
+
+def log_bucket_starts(num_buckets: int, max_distance: float) -> List[int]:
+    """Smallest distance that falls into every bucket of a table whose first half is exact and whose second half is
+    logarithmic up to `max_distance`: bucket(n) = n for n < B/2, else
+    min(B - 1, B/2 + floor(ln(n / (B/2)) / ln(max_distance / (B/2)) * (B - B/2)))."""
+    B, half = num_buckets, num_buckets // 2
+
+    def bucket(n: int) -> int:
+        if n < half:
+            return n
+        return min(B - 1, half + int(math.floor(math.log(n / half) / math.log(max_distance / half) * (B - half))))
+
+    starts = list(range(half)) + [0] * (B - half)
+    n = half
+    for b in range(half, B):
+        while bucket(n) < b:
+            n += 1
+        starts[b] = n
+    return starts
+
+
+# ------------------------------------------------------------------------------------------------ short convolution
+def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, meta: RaggedMeta,
+                    activation: bool = True) -> torch.Tensor:
+    """x [T, C] (may be a column slice, unit stride inside a row); weight [C, taps], last column = current token;
+    state [slots, taps - 1, C] = the last inputs of every sequence, read and advanced.  Returns silu(conv) [T, C]."""
+    T, C = x.shape
+    taps = weight.shape[1]
+    out = torch.empty(T, C, dtype=x.dtype, device=x.device)
+    if use_native(x):
+        assert x.stride(1) == 1 and weight.is_contiguous() and state.is_contiguous() and state.dtype == x.dtype
+        loader.check(_get_lib().cb_short_conv_silu(
+            loader.ptr(x), _i64(x.stride(0)), loader.ptr(weight), loader.ptr(state), loader.ptr(out), _i64(C),
+            loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len), loader.ptr(meta.slots), meta.nseq, meta.max_q, C, taps,
+            int(activation), 1, code(x.dtype), loader.stream_ptr()), "short_conv_silu")
+        loader.launch_counter.add("short_conv_silu", 2)
+        return out
+    t0 = 0
+    w = weight.float()
+    for n, c, slot in zip(meta.q_lens, meta.ctx_lens, meta.slot_list):
+        if n == 0:
+            continue
+        prev = state[slot].float() if c > 0 else torch.zeros(taps - 1, C)
+        full = torch.cat([prev, x[t0:t0 + n].float()], 0)                     # [taps - 1 + n, C]
+        acc = torch.zeros(n, C)
+        for i in range(taps):
+            acc += full[i:i + n] * w[:, i]
+        out[t0:t0 + n] = (F.silu(acc) if activation else acc).to(x.dtype)
+        if taps > 1:
+            state[slot] = full[n:].to(state.dtype)
+        t0 += n
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ state scans
+def _scan_native(mode, q, k, v, araw, braw, head_decay, a_log, dt_bias, state, meta, heads, qk_heads, dim, vdim,
+                 act_silu, unit_qk, unit_eps, q_scale):
+    T = q.shape[0]
+    out = torch.empty(T, heads * vdim, dtype=torch.float32, device=q.device)
+    for t in (q, k, v):
+        assert t.stride(1) == 1
+    assert state.dtype == torch.float32 and state.is_contiguous()
+    ld = lambda t: _i64(0 if t is None else t.stride(0))
+    loader.check(_get_lib().cb_state_scan(
+        mode, loader.ptr(q), ld(q), loader.ptr(k), ld(k), loader.ptr(v), ld(v), loader.ptr(araw), ld(araw),
+        loader.ptr(braw), ld(braw), loader.ptr(head_decay), loader.ptr(a_log), loader.ptr(dt_bias), loader.ptr(state),
+        loader.ptr(out), loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len), loader.ptr(meta.slots), meta.nseq, heads,
+        qk_heads, dim, vdim, int(act_silu), int(unit_qk), _f(unit_eps), _f(q_scale), code(q.dtype),
+        loader.stream_ptr()), "state_scan")
+    loader.launch_counter.add("state_scan")
+    return out
+
+
+def state_scan_decay(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, head_decay: torch.Tensor, state: torch.Tensor,
+                     meta: RaggedMeta, heads: int, dim: int, vdim: int, act_silu: bool = True) -> torch.Tensor:
+    """Decayed outer-product memory per head: S <- decay_h S + k v^T, o = S^T q (q, k, v through silu first when
+    `act_silu`).  q, k [T, heads x dim], v [T, heads x vdim]; state [slots, heads, dim, vdim] fp32.  Returns fp32 o."""
+    if dim > 128:
+        raise NotImplementedError("state_scan: key width above 128 is not supported")
+    if use_native(q):
+        return _scan_native(0, q, k, v, None, None, head_decay, None, None, state, meta, heads, heads, dim, vdim,
+                            act_silu, False, 0.0, 1.0)
+    T = q.shape[0]
+    out = torch.empty(T, heads * vdim, dtype=torch.float32)
+    act = F.silu if act_silu else (lambda z: z)
+    t0 = 0
+    dec = head_decay.float()[:, None, None]
+    for n, c, slot in zip(meta.q_lens, meta.ctx_lens, meta.slot_list):
+        if n == 0:
+            continue
+        S = state[slot].clone() if c > 0 else torch.zeros_like(state[slot])
+        qq = act(q[t0:t0 + n].float()).view(n, heads, dim)
+        kk = act(k[t0:t0 + n].float()).view(n, heads, dim)
+        vv = act(v[t0:t0 + n].float()).view(n, heads, vdim)
+        for t in range(n):
+            S = dec * S + kk[t][:, :, None] * vv[t][:, None, :]
+            out[t0 + t] = torch.einsum("hdv,hd->hv", S, qq[t]).reshape(-1)
+        state[slot] = S
+        t0 += n
+    return out
+
+
+def state_scan_delta(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_pre: torch.Tensor, beta_pre: torch.Tensor,
+                     a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, meta: RaggedMeta, heads: int,
+                     qk_heads: int, dim: int, vdim: int, unit_eps: float = 1e-6,
+                     q_scale: Optional[float] = None) -> torch.Tensor:
+    """Gated delta rule with one decay per head and key channel.  Per token and head: q, k -> unit vectors (q also times
+    `q_scale`), g = exp(-exp(a_log_h) softplus(decay_pre + dt_bias)), beta = sigmoid(beta_pre);
+    S <- g S (rows); u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  q, k [T, qk_heads x dim] (head h reads
+    h // (heads / qk_heads)), v [T, heads x vdim], decay_pre [T, heads x dim], beta_pre [T, heads]; fp32 state."""
+    if dim > 128:
+        raise NotImplementedError("state_scan: key width above 128 is not supported")
+    q_scale = dim ** -0.5 if q_scale is None else q_scale
+    if use_native(q):
+        return _scan_native(1, q, k, v, decay_pre, beta_pre, None, a_log, dt_bias, state, meta, heads, qk_heads, dim,
+                            vdim, False, True, unit_eps, q_scale)
+    T = q.shape[0]
+    out = torch.empty(T, heads * vdim, dtype=torch.float32)
+    rep = heads // qk_heads
+    A = a_log.float().exp()[None, :, None]
+    t0 = 0
+    for n, c, slot in zip(meta.q_lens, meta.ctx_lens, meta.slot_list):
+        if n == 0:
+            continue
+        S = state[slot].clone() if c > 0 else torch.zeros_like(state[slot])
+        qq = q[t0:t0 + n].float().view(n, qk_heads, dim)
+        kk = k[t0:t0 + n].float().view(n, qk_heads, dim)
+        qq = qq / torch.sqrt((qq * qq).sum(-1, keepdim=True) + unit_eps) * q_scale
+        kk = kk / torch.sqrt((kk * kk).sum(-1, keepdim=True) + unit_eps)
+        qq, kk = qq.repeat_interleave(rep, 1), kk.repeat_interleave(rep, 1)
+        vv = v[t0:t0 + n].float().view(n, heads, vdim)
+        g = torch.exp(-A * F.softplus(decay_pre[t0:t0 + n].float().view(n, heads, dim)
+                                      + dt_bias.float().view(1, heads, dim)))
+        beta = torch.sigmoid(beta_pre[t0:t0 + n].float())
+        for t in range(n):
+            S = g[t][:, :, None] * S
+            u = beta[t][:, None] * (vv[t] - torch.einsum("hdv,hd->hv", S, kk[t]))
+            S = S + kk[t][:, :, None] * u[:, None, :]
+            out[t0 + t] = torch.einsum("hdv,hd->hv", S, qq[t]).reshape(-1)
+        state[slot] = S
+        t0 += n
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ norms
+def gated_group_rms_norm(o: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], group: int, eps: float,
+                         out_dtype: torch.dtype) -> torch.Tensor:
+    """o [T, C] fp32 -> o / sqrt(mean over each group of `group` channels + eps) * weight[c % len(weight)]
+    * sigmoid(gate), in `out_dtype`."""
+    T, C = o.shape
+    if use_native(o):
+        out = torch.empty(T, C, dtype=out_dtype, device=o.device)
+        assert o.is_contiguous() and weight.dtype == out_dtype and (gate is None or gate.stride(1) == 1)
+        loader.check(_get_lib().cb_gated_group_rmsnorm(
+            loader.ptr(o), loader.ptr(weight), weight.numel(), loader.ptr(gate), _i64(0 if gate is None else gate.stride(0)),
+            loader.ptr(out), _i64(T), C, group, _f(eps), code(out_dtype), loader.stream_ptr()), "gated_group_rmsnorm")
+        loader.launch_counter.add("gated_group_rmsnorm")
+        return out
+    y = o.view(T, C // group, group)
+    y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)
+    y = y.reshape(T, C) * weight.float().repeat(C // weight.numel())
+    if gate is not None:
+        y = y * torch.sigmoid(gate.float())
+    return y.to(out_dtype)
+
+
+def rms_norm_residual(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, mult: float = 1.0,
+                      offset: float = 0.0, want_cast: bool = True) -> Optional[torch.Tensor]:
+    """x [T, W] fp32, updated in place: x += mult * y / rms(y) * (offset + weight).  Returns x in y's dtype."""
+    T, W = x.shape
+    assert x.dtype == torch.float32
+    if use_native(x):
+        assert x.is_contiguous() and y.stride(1) == 1 and weight.dtype == y.dtype
+        h = torch.empty(T, W, dtype=y.dtype, device=x.device) if want_cast else None
+        loader.check(_get_lib().cb_rmsnorm_residual(loader.ptr(x), loader.ptr(y), _i64(y.stride(0)), loader.ptr(weight),
+                                                    loader.ptr(h), _i64(T), W, _f(eps), _f(mult), _f(offset),
+                                                    code(y.dtype), loader.stream_ptr()), "rmsnorm_residual")
+        loader.launch_counter.add("rmsnorm_residual")
+        return h
+    yf = y.float()
+    x += mult * (yf / torch.sqrt((yf * yf).mean(-1, keepdim=True) + eps) * (offset + weight.float()))
+    return x.to(y.dtype) if want_cast else None
+
+
+def rms_norm_f32in(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float = 0.0) -> torch.Tensor:
+    """x [T, W] fp32 -> x / rms(x) * (offset + weight) in the weight's dtype."""
+    T, W = x.shape
+    if use_native(x):
+        out = torch.empty(T, W, dtype=weight.dtype, device=x.device)
+        loader.check(_get_lib().cb_rmsnorm_f32in(loader.ptr(x.contiguous()), loader.ptr(weight), loader.ptr(out), _i64(T), W,
+                                                 _f(eps), _f(offset), code(weight.dtype), loader.stream_ptr()),
+                     "rmsnorm_f32in")
+        loader.launch_counter.add("rmsnorm_f32in")
+        return out
+    xf = x.float()
+    return (xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps) * (offset + weight.float())).to(weight.dtype)
+
+
+# ------------------------------------------------------------------------------------------------ paged attention
+def paged_kv_write_mix(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                       block_tables: torch.Tensor, meta: RaggedMeta, v_other: Optional[torch.Tensor] = None,
+                       lam: float = 0.0) -> None:
+    """k [T, Gk x dim], v [T, Gv x vdim] rows into caches [blocks, block_size, G, dim] / [.., G, vdim]; with `v_other`
+    the stored values are (1 - lam) v + lam v_other."""
+    T = k.shape[0]
+    bs = k_cache.shape[1]
+    kw, vw = k.shape[1], v.shape[1]
+    if use_native(k):
+        assert k.stride(1) == 1 and v.stride(1) == 1 and k_cache.dtype == k.dtype and v_cache.dtype == v.dtype
+        loader.check(_get_lib().cb_paged_kv_write_mix(
+            loader.ptr(k), _i64(k.stride(0)), loader.ptr(v), _i64(v.stride(0)), loader.ptr(v_other),
+            _i64(0 if v_other is None else v_other.stride(0)), _f(lam), loader.ptr(k_cache), loader.ptr(v_cache),
+            loader.ptr(block_tables), loader.ptr(meta.token_seq), loader.ptr(meta.token_pos), _i64(T), kw, vw, bs,
+            block_tables.shape[1], code(k.dtype), loader.stream_ptr()), "paged_kv_write_mix")
+        loader.launch_counter.add("paged_kv_write_mix")
+        return
+    if v_other is not None:
+        v = ((1.0 - lam) * v.float() + lam * v_other.float()).to(v.dtype)
+    blk = block_tables[meta.token_seq.long(), (meta.token_pos // bs).long()].long()
+    off = (meta.token_pos % bs).long()
+    k_cache.view(k_cache.shape[0], bs, kw)[blk, off] = k
+    v_cache.view(v_cache.shape[0], bs, vw)[blk, off] = v
+
+
+def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                         meta: RaggedMeta, scale: float, bias_table: Optional[torch.Tensor] = None,
+                         bucket_starts: Optional[torch.Tensor] = None, sink: bool = False) -> torch.Tensor:
+    """Causal attention of every step token over positions 0..pos of its sequence in the paged cache.
+    q [T, heads x dim]; caches [blocks, block_size, kv_heads, dim | vdim]; bias_table [buckets, heads] fp32 indexed by
+    the bucket of the distance (`bucket_starts` [buckets] int32: smallest distance of each bucket); `sink` adds a key of
+    score 0 without a value to the softmax.  Returns [T, heads x vdim]."""
+    T = q.shape[0]
+    _, bs, G, dim = k_cache.shape
+    vdim = v_cache.shape[3]
+    heads = q.shape[1] // dim
+    nb = 0 if bias_table is None else bias_table.shape[0]
+    if use_native(q):
+        if vdim > 256:
+            raise NotImplementedError("paged_bias_attention: value width above 256 is not supported")
+        assert q.stride(1) == 1 and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
+        out = torch.empty(T, heads * vdim, dtype=q.dtype, device=q.device)
+        loader.check(_get_lib().cb_paged_bias_attention(
+            loader.ptr(q), _i64(q.stride(0)), loader.ptr(k_cache), loader.ptr(v_cache), loader.ptr(block_tables),
+            loader.ptr(meta.token_seq), loader.ptr(meta.token_pos), loader.ptr(bias_table), loader.ptr(bucket_starts), nb,
+            loader.ptr(out), _i64(T), heads, G, dim, vdim, bs, block_tables.shape[1], _f(scale), int(sink),
+            code(q.dtype), loader.stream_ptr()), "paged_bias_attention")
+        loader.launch_counter.add("paged_bias_attention")
+        return out
+    out = torch.empty(T, heads * vdim, dtype=q.dtype)
+    rep = heads // G
+    t0 = 0
+    for i, (n, c) in enumerate(zip(meta.q_lens, meta.ctx_lens)):
+        if n == 0:
+            continue
+        L = c + n
+        blks = block_tables[i, :(L + bs - 1) // bs].long()
+        kk = k_cache[blks].reshape(-1, G, dim)[:L].float().repeat_interleave(rep, 1)
+        vv = v_cache[blks].reshape(-1, G, vdim)[:L].float().repeat_interleave(rep, 1)
+        qq = q[t0:t0 + n].float().view(n, heads, dim)
+        s = torch.einsum("ihd,jhd->hij", qq, kk) * scale
+        dist = torch.arange(c, L)[:, None] - torch.arange(L)[None, :]
+        if bias_table is not None:
+            b = torch.bucketize(dist.clamp(min=0), bucket_starts.to(torch.int64), right=True) - 1
+            s = s + bias_table.float()[b].permute(2, 0, 1)
+        s = s.masked_fill(dist[None] < 0, float("-inf"))
+        if sink:
+            s = torch.cat([s, torch.zeros(heads, n, 1)], -1)
+        p = torch.softmax(s, -1)[..., :L]
+        out[t0:t0 + n] = torch.einsum("hij,jhv->ihv", p, vv).reshape(n, heads * vdim).to(q.dtype)
+        t0 += n
+    return out
