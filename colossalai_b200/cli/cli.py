@@ -1,4 +1,5 @@
-"""`colossalai_b200` command line: `run` (launcher) and `check` (installation report).
+"""`colossalai_b200` command line: `run` (launcher), `check` (installation report) and `replay`
+(token traces through the serving engine).
 Parity: reference `colossalai/cli/cli.py` (click group with `run`, `check`); argparse here (click is not required)."""
 from __future__ import annotations
 
@@ -12,9 +13,11 @@ def build_parser() -> argparse.ArgumentParser:
     sub = parser.add_subparsers(dest="command")
     from .check import add_check_parser
     from .launcher import add_run_parser
+    from .replay import add_replay_parser
 
     add_run_parser(sub)
     add_check_parser(sub)
+    add_replay_parser(sub)
     return parser
 
 

@@ -129,6 +129,11 @@ class InferenceConfig(RPC_PARAM):
     patched_parallelism_size: int = 1
     ignore_eos: bool = False
     use_spec_dec: bool = False
+    # ragged steps: portions of prompts run beside single decoded tokens under one token budget per step (always on
+    # for hybrid decoders, whose recurrent layers carry state from portion to portion)
+    enable_chunked_prefill: bool = False
+    max_num_batched_tokens: int = 2048
+    max_cache_tokens: Optional[int] = None      # size the page pool for this many live tokens instead of the worst case
 
     def __post_init__(self) -> None:
         self.max_context_len_to_capture = self.max_input_len + self.max_output_len

@@ -27,7 +27,7 @@ from ..sampler import search_tokens
 from ..spec import Drafter, GlideInput
 from ..struct import Sequence
 from .base_engine import BaseEngine
-from .request_handler import RequestHandler
+from .request_handler import RaggedRequestHandler, RequestHandler
 
 __all__ = ["LLMEngine"]
 
@@ -68,12 +68,23 @@ class LLMEngine(BaseEngine):
         self.tokenizer = tokenizer or _SimpleTokenizer()
         self.generation_config = self.inference_config.to_generation_config(self.model_config)
         self.generation_config_dict = self.generation_config.to_dict()
-        self.request_handler = RequestHandler(self.inference_config, self.model_config)
-        k_caches, v_caches = self.request_handler.get_kvcache()
-        self.kv_runtime = PagedKVRuntime(k_caches, v_caches, self.inference_config.block_size)
-        self._init_decode_workspace(k_caches)
+        # hybrid decoders (per-layer mixers, recurrent state) and chunked prefill run ragged steps
+        self.ragged_mode = self.inference_config.enable_chunked_prefill or \
+            getattr(self.model_config, "layer_specs", None) is not None
+        if self.ragged_mode:
+            assert self.inference_config.tp_size == 1, "ragged steps are single-GPU for now"
+            self.request_handler = RaggedRequestHandler(self.inference_config, self.model_config)
+            k_caches, v_caches = self.request_handler.get_kvcache()
+            self.kv_runtime = PagedKVRuntime(k_caches, v_caches, self.inference_config.block_size,
+                                             states=self.request_handler.state_manager.states)
+        else:
+            self.request_handler = RequestHandler(self.inference_config, self.model_config)
+            k_caches, v_caches = self.request_handler.get_kvcache()
+            self.kv_runtime = PagedKVRuntime(k_caches, v_caches, self.inference_config.block_size)
+            self._init_decode_workspace(k_caches)
         self.counter = count()
-        self.use_cuda_graph = self.inference_config.use_cuda_graph and torch.cuda.is_available()
+        self.use_cuda_graph = self.inference_config.use_cuda_graph and torch.cuda.is_available() \
+            and not self.ragged_mode
         if self.use_cuda_graph and (self.model_config.head_dim not in (64, 128, 256)
                                     or self.dtype not in (torch.float16, torch.bfloat16)):
             # the decode step must stay on the native paged kernel to be capturable (the reference path syncs)
@@ -364,8 +375,60 @@ class LLMEngine(BaseEngine):
         self.request_handler.append_next_tokens(next_tokens.cpu())
         return self.request_handler.update()
 
+    # ------------------------------------------------------------------ ragged steps
+    @torch.inference_mode()
+    def forward_ragged(self, entries, want: Optional[List[List[int]]] = None) -> torch.Tensor:
+        """The step function of ragged mode.  `entries`: [(RaggedSeq, next tokens)], all run as one batch - portions of
+        prompts beside single decoded tokens - from the cache and state that earlier steps left.  `want[i]`: places
+        among entry i's tokens whose logits are returned (default: its last token).  Returns fp32 logits
+        [rows, vocab] in the order of the entries and of `want`."""
+        handler = self.request_handler
+        entries = [(rs, list(toks)) for rs, toks in entries if len(toks) > 0] if want is None else \
+            [(rs, list(toks)) for rs, toks in entries]
+        if want is None:
+            want = [[len(toks) - 1] for _, toks in entries]
+        for rs, toks in entries:
+            handler.reserve(rs, len(toks))
+        q_lens = [len(toks) for _, toks in entries]
+        rows, base = [], 0
+        for n, w in zip(q_lens, want):
+            rows += [base + int(j) for j in w]
+            base += n
+        flat = [t for _, toks in entries for t in toks]
+        if not flat:
+            return torch.empty(0, self.model_config.vocab_size, dtype=torch.float32, device=self.device)
+        input_ids = torch.tensor(flat, dtype=torch.long).to(self.device, non_blocking=True)
+        tables = torch.stack([rs.block_table for rs, _ in entries])
+        positions = self.kv_runtime.set_ragged_step(tables, q_lens, [rs.ctx_len for rs, _ in entries],
+                                                    [rs.slot for rs, _ in entries], self.device)
+        from ...models.transformer import SeqMeta
+
+        meta = SeqMeta(batch=1, seqlen=len(flat), positions=positions)
+        sel = torch.tensor(rows, dtype=torch.long).to(self.device, non_blocking=True)
+        out = self.model(input_ids=input_ids.view(1, -1), kv_cache=self.kv_runtime, meta=meta, logit_positions=sel)
+        for (rs, _), n in zip(entries, q_lens):
+            rs.ctx_len += n
+        return out["logits"][:, : self.model_config.vocab_size].float()
+
+    def _step_ragged(self) -> List[Sequence]:
+        handler = self.request_handler
+        entries = handler.schedule()
+        if not entries:
+            return []
+        logits = self.forward_ragged(entries)
+        sampling = [i for i, (rs, _) in enumerate(entries) if rs.prompt_done]       # ctx_len advanced: prompt consumed
+        if not sampling:
+            return []
+        idx = torch.tensor(sampling, dtype=torch.long, device=logits.device)
+        ids = [entries[i][0].seq.input_token_id + entries[i][0].seq.output_token_id for i in sampling]
+        next_tokens = search_tokens(self.generation_config, logits.index_select(0, idx), False,
+                                    batch_token_ids=ids).tolist()
+        return handler.update({entries[i][0].request_id: t for i, t in zip(sampling, next_tokens)})
+
     @torch.inference_mode()
     def step(self) -> List[Sequence]:
+        if self.ragged_mode:
+            return self._step_ragged()
         batch = self.request_handler.schedule()
         if batch.is_empty:
             return self.request_handler.update()

@@ -17,7 +17,7 @@ from ..kv_cache import KVCacheManager
 from ..sampler import search_tokens
 from ..struct import RequestStatus, Sequence
 
-__all__ = ["RunningList", "RequestHandler", "NaiveRequestHandler"]
+__all__ = ["RunningList", "RequestHandler", "NaiveRequestHandler", "RaggedSeq", "RaggedRequestHandler"]
 
 logger = get_dist_logger(__name__)
 
@@ -289,6 +289,149 @@ class RequestHandler(NaiveRequestHandler):
 
     def streamingllm_free_block_tables(self, updated_block_ids: List[int]) -> None:
         self.cache_manager.streamingllm_free_block_tables(updated_block_ids)
+
+
+class RaggedSeq:
+    """A live sequence of the ragged scheduler: its state slot, its row of page ids and how far it has been consumed."""
+
+    def __init__(self, seq: Sequence, slot: int, max_blocks: int) -> None:
+        self.seq = seq
+        self.slot = slot
+        self.block_table = torch.full((max_blocks,), -1, dtype=torch.int32)
+        self.ctx_len = 0                 # tokens whose K / V and state updates are in the cache
+        self.promised = 0                # pages held back for it in the pool and not taken yet
+
+    @property
+    def request_id(self):
+        return self.seq.request_id
+
+    @property
+    def prompt_done(self) -> bool:
+        return self.ctx_len >= self.seq.input_len
+
+
+class RaggedRequestHandler(NaiveRequestHandler):
+    """Token-budget scheduler for ragged steps (chunked prefill): every step takes one token of each decoding sequence
+    and fills the rest of `max_num_batched_tokens` with portions of prompts, admitting waiting requests while a state
+    slot and pages for their whole length are free.  Pages come from `KVCacheManager`, recurrent state slots from
+    `StateCacheManager`; both go back when a sequence ends.
+
+    The reference's scheduler (`colossalai/inference/core/request_handler.py`) runs whole prompts in a bucket of their
+    own; recurrent layers and long prompts want portions, so this handler sits beside it."""
+
+    def __init__(self, inference_config: InferenceConfig, model_config) -> None:
+        super().__init__()
+        from ..kv_cache import StateCacheManager
+
+        self.inference_config = inference_config
+        self.cache_manager = KVCacheManager(inference_config, model_config)
+        self.state_manager = StateCacheManager(inference_config, model_config)
+        self.block_size = inference_config.block_size
+        self.max_tokens = max(int(inference_config.max_num_batched_tokens), 1)
+        self.live: Dict[object, RaggedSeq] = {}
+        self.waiting_list: List[Sequence] = []
+        self.done_list: List[Sequence] = []
+        self._promised = 0               # pages promised to live sequences and not taken yet
+
+    # ------------------------------------------------------------------ pool
+    def get_kvcache(self):
+        return self.cache_manager.get_kv_cache()
+
+    def _pages(self, tokens: int) -> int:
+        return (tokens + self.block_size - 1) // self.block_size
+
+    def can_admit(self, total_len: int) -> bool:
+        return (self.state_manager.num_available_slots > 0
+                and self._pages(total_len) <= self.cache_manager.num_available_blocks - self._promised
+                and self._pages(total_len) <= self.cache_manager.get_max_blocks_per_sequence())
+
+    def admit(self, seq: Sequence, total_len: Optional[int] = None) -> RaggedSeq:
+        """Give `seq` a state slot and an (empty) page table.  `total_len`: pages to hold back for it (None: none)."""
+        assert seq.request_id not in self.live, f"Sequence {seq.request_id} already exists."
+        rs = RaggedSeq(seq, self.state_manager.allocate(), self.cache_manager.get_max_blocks_per_sequence())
+        rs.promised = self._pages(total_len) if total_len else 0
+        self._promised += rs.promised
+        self.live[seq.request_id] = rs
+        if seq.status in (RequestStatus.WAITING, RequestStatus.RECYCLED):
+            seq.mark_running()
+        return rs
+
+    def reserve(self, rs: RaggedSeq, n: int) -> None:
+        """Pages for the next `n` tokens of `rs`."""
+        before = self.cache_manager.num_available_blocks
+        for j in range(n):
+            pos = rs.ctx_len + j
+            if pos % self.block_size == 0 or j == 0:
+                self.cache_manager.allocate_single_block(rs.block_table, pos // self.block_size)
+        took = before - self.cache_manager.num_available_blocks
+        give = min(took, rs.promised)
+        rs.promised -= give
+        self._promised -= give
+
+    def release(self, request_id) -> None:
+        rs = self.live.pop(request_id)
+        self.cache_manager.free_block_table(rs.block_table)
+        self.state_manager.free(rs.slot)
+        self._promised -= rs.promised
+        rs.promised = 0
+
+    # ------------------------------------------------------------------ scheduling
+    def add_sequence(self, req: Sequence) -> None:
+        assert req.request_id not in self.live and all(s.request_id != req.request_id for s in self.waiting_list), \
+            f"Sequence {req.request_id} already exists."
+        self.waiting_list.append(req)
+
+    def abort_sequence(self, request_id) -> None:
+        for s in list(self.waiting_list):
+            if s.request_id == request_id:
+                self.waiting_list.remove(s)
+                s.mark_aborted()
+        if request_id in self.live:
+            self.live[request_id].seq.mark_aborted()
+            self.release(request_id)
+
+    def check_unfinished_reqs(self) -> bool:
+        return bool(self.waiting_list) or bool(self.live)
+
+    def schedule(self) -> List:
+        """[(RaggedSeq, tokens)] of the next step."""
+        while self.waiting_list:
+            seq = self.waiting_list[0]
+            total = seq.input_len + seq.max_output_len
+            if total > self.cache_manager.get_max_blocks_per_sequence() * self.block_size or \
+                    self._pages(total) > self.cache_manager.total_num_blocks:
+                self.waiting_list.pop(0)
+                logger.warning(f"request {seq.request_id} cannot fit the cache; aborted")
+                seq.mark_aborted()
+                self.done_list.append(seq)
+                continue
+            if not self.can_admit(total):
+                break
+            self.admit(self.waiting_list.pop(0), total)
+        budget = self.max_tokens
+        entries = []
+        for rs in self.live.values():                 # one token of every decoding sequence
+            if rs.prompt_done and budget > 0:
+                entries.append((rs, [rs.seq.output_token_id[-1]]))
+                budget -= 1
+        for rs in self.live.values():                 # then portions of prompts
+            if not rs.prompt_done and budget > 0:
+                n = min(budget, rs.seq.input_len - rs.ctx_len)
+                entries.append((rs, rs.seq.input_token_id[rs.ctx_len: rs.ctx_len + n]))
+                budget -= n
+        return entries
+
+    def update(self, sampled: Dict[object, int]) -> List[Sequence]:
+        """Append the sampled token of every sequence that produced one; collect and free the finished ones."""
+        finished = []
+        for rid, tok in sampled.items():
+            rs = self.live[rid]
+            rs.seq.output_token_id.append(int(tok))
+            if rs.seq.check_finish():
+                finished.append(rs.seq)
+                self.release(rid)
+        self.done_list.extend(finished)
+        return finished
 
 
 class RPCRequestHandler(RequestHandler):
