@@ -40,8 +40,8 @@ def layer_state_shapes(model_config, layer: int, slots: int) -> Optional[Dict[st
     if sp is None or not sp.recurrent:
         return None
     out = {"S": (slots, sp.heads, sp.dim, sp.vdim)}
-    if sp.conv > 1:
-        out["conv"] = (slots, sp.conv - 1, 2 * sp.kv_heads * sp.dim + sp.heads * sp.vdim)
+    if sp.kind == "channel_delta":        # a one-tap convolution carries nothing: an empty tensor keeps the call uniform
+        out["conv"] = (slots, max(sp.conv - 1, 0), 2 * sp.kv_heads * sp.dim + sp.heads * sp.vdim)
     return out
 
 
