@@ -43,6 +43,10 @@ def parse_args():
     p.add_argument("--steps", type=int, default=5)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--workload", default="train", choices=["train", "hybrid-serve"],
+                   help="train: the headline training step (default, the contract above).  hybrid-serve: prefill / decode "
+                        "throughput of the hybrid decoder beside Llama at equal size and its kernels against their "
+                        "rooflines (examples/inference/benchmark_hybrid.py; extra flags are passed on)")
     p.add_argument("--model", default=os.environ.get("CB200_BENCH_MODEL", "llama3-8b"))
     p.add_argument("--seq", type=int, default=4096)
     p.add_argument("--mbs", type=int, default=1, help="sequences per GPU per step (weak scaling)")
@@ -378,6 +382,13 @@ def run_reference(args) -> None:
 
 
 def main():
+    if "hybrid-serve" in sys.argv:
+        i = sys.argv.index("hybrid-serve")
+        if i > 0 and sys.argv[i - 1] == "--workload":
+            sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "examples", "inference"))
+            import benchmark_hybrid
+
+            return benchmark_hybrid.main(sys.argv[1: i - 1] + sys.argv[i + 1:])
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -422,6 +422,216 @@ __global__ void __launch_bounds__(128) paged_bias_attention_kernel(
   }
 }
 
+// ------------------------------------------------------------------------------------------------ tensor-core variant
+// 16-bit inputs: a CTA of 4 warps owns 64 query ROWS of one (sequence, kv head): row = (token of the portion, query head
+// of the kv head's group), so the K / V tile that cp.async brings from the pages is shared by the whole group and a
+// decoded token fills rows with its group's heads.  S = Q K^T and O += P V run on mma.sync m16n8k16 with fp32
+// accumulators; softmax, bias and sink in fp32 registers.  D = head width rounded up (zero padded in shared memory).
+constexpr int MMA_BM = 64, MMA_BN = 64;
+
+template <typename T> CB_DEVICE void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <> CB_DEVICE void mma_16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> CB_DEVICE void mma_16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T> CB_DEVICE uint32_t pack2(float lo, float hi);
+template <> CB_DEVICE uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> CB_DEVICE uint32_t pack2<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+CB_DEVICE float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+CB_DEVICE void cp_async16(void* smem_dst, const void* gmem_src, uint32_t src_bytes) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(src_bytes) : "memory");
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(128) paged_bias_attention_mma_kernel(
+    const T* __restrict__ q, int64_t ldq, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+    const int* __restrict__ block_tables, const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
+    const float* __restrict__ bias_table, const uint8_t* __restrict__ lut, int lut_n, int nbuckets, T* __restrict__ out,
+    int heads, int kv_heads, int dim, int vdim, int block_size, int max_blocks, float scale, int sink) {
+  constexpr int LDS = D + 8;                    // padded row: 16-byte aligned, conflict-free fragment reads
+  constexpr float LOG2E = 1.4426950408889634f;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* Ks = reinterpret_cast<T*>(smem_raw);
+  T* Vs = Ks + MMA_BN * LDS;
+  float* tab = reinterpret_cast<float*>(Vs + MMA_BN * LDS);          // [nbuckets][R] of this kv head's group
+  const int s = blockIdx.z, g = blockIdx.y;
+  const int R = heads / kv_heads;
+  const int t0 = cu_q[s], qlen = cu_q[s + 1] - t0;
+  const int nrows = qlen * R, row0 = blockIdx.x * MMA_BM;
+  if (row0 >= nrows) return;
+  const int ctx = ctx_len[s];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+  for (int i = tid; i < nbuckets * R; i += blockDim.x) tab[i] = bias_table[(i / R) * heads + g * R + (i % R)] * LOG2E;
+  const int* bt = block_tables + (int64_t)s * max_blocks;
+
+  int rr[2], pos[2], hr[2];
+  bool valid[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    rr[e] = row0 + warp * 16 + gid + 8 * e;
+    valid[e] = rr[e] < nrows;
+    hr[e] = valid[e] ? rr[e] % R : 0;
+    pos[e] = valid[e] ? ctx + rr[e] / R : -1;
+  }
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int r = e & 1, col = ks * 16 + tig * 2 + ((e >> 1) ? 8 : 0);
+      uint32_t val = 0;
+      if (valid[r] && col < dim)
+        val = *reinterpret_cast<const uint32_t*>(q + (int64_t)(t0 + rr[r] / R) * ldq + (g * R + hr[r]) * dim + col);
+      qf[ks][e] = val;
+    }
+  float o[D / 8][4];
+#pragma unroll
+  for (int nv = 0; nv < D / 8; ++nv)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nv][e] = 0.f;
+  float m[2], l[2];
+  m[0] = m[1] = sink ? 0.f : -INFINITY;         // log2 domain (0 either way)
+  l[0] = l[1] = 0.f;                            // per-thread partial; the sink's 1 is added once at the end
+  const float sc2 = scale * LOG2E;
+  const int last_row = min(nrows - 1, row0 + MMA_BM - 1);
+  const int pos_max = ctx + last_row / R;
+
+  for (int j0 = 0; j0 <= pos_max; j0 += MMA_BN) {
+    __syncthreads();                            // previous tile fully consumed (and `tab` visible on the first pass)
+    constexpr int CH = D / 8;
+    for (int idx = tid; idx < MMA_BN * CH; idx += blockDim.x) {
+      const int r = idx / CH, c8 = (idx % CH) * 8;
+      const int j = j0 + r;
+      const bool in = j <= pos_max;
+      const int64_t row = in ? ((int64_t)bt[j / block_size] * block_size + j % block_size) * kv_heads + g : 0;
+      const bool kin = in && c8 < dim, vin = in && c8 < vdim;
+      cp_async16(Ks + r * LDS + c8, k_cache + (kin ? row * dim + c8 : 0), kin ? 16u : 0u);
+      cp_async16(Vs + r * LDS + c8, v_cache + (vin ? row * vdim + c8 : 0), vin ? 16u : 0u);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    const int wmax = ctx + min(nrows - 1, row0 + warp * 16 + 15) / R;     // last position any row of this warp sees
+    if (j0 > wmax) continue;                                              // warp-uniform: whole tile masked
+    float sacc[MMA_BN / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < MMA_BN / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sacc[nt][e] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const T* kp = Ks + (nt * 8 + gid) * LDS + ks * 16 + tig * 2;
+        mma_16816<T>(sacc[nt], qf[ks], *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+      }
+    }
+    float mx[2] = {m[0], m[1]};
+#pragma unroll
+    for (int nt = 0; nt < MMA_BN / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1, j = j0 + nt * 8 + tig * 2 + (e & 1);
+        float sv = -INFINITY;
+        if (j <= pos[r]) {
+          sv = sacc[nt][e] * sc2;
+          if (nbuckets > 0) {
+            const int n = pos[r] - j;
+            const int b = n < lut_n ? (int)__ldg(lut + n) : nbuckets - 1;
+            sv += tab[b * R + hr[r]];
+          }
+        }
+        sacc[nt][e] = sv;
+        mx[r] = fmaxf(mx[r], sv);
+      }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float mu = mx[r] == -INFINITY ? 0.f : mx[r];
+      alpha[r] = ex2f(m[r] - mu);                 // m = -inf -> 0
+      m[r] = mx[r];
+      l[r] *= alpha[r];
+      mx[r] = mu;
+    }
+#pragma unroll
+    for (int nv = 0; nv < D / 8; ++nv) {
+      o[nv][0] *= alpha[0]; o[nv][1] *= alpha[0];
+      o[nv][2] *= alpha[1]; o[nv][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int nt = 0; nt < MMA_BN / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = ex2f(sacc[nt][e] - mx[e >> 1]);
+        sacc[nt][e] = p;
+        l[e >> 1] += p;
+      }
+#pragma unroll
+    for (int kk = 0; kk < MMA_BN / 16; ++kk) {
+      uint32_t pa[4];
+      pa[0] = pack2<T>(sacc[2 * kk][0], sacc[2 * kk][1]);
+      pa[1] = pack2<T>(sacc[2 * kk][2], sacc[2 * kk][3]);
+      pa[2] = pack2<T>(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
+      pa[3] = pack2<T>(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+      const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(Vs + (kk * 16 + (lane & 15)) * LDS);
+#pragma unroll
+      for (int nv = 0; nv < D / 8; ++nv) {
+        uint32_t b0, b1;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                     : "=r"(b0), "=r"(b1) : "r"(vrow + nv * 16));
+        mma_16816<T>(o[nv], pa, b0, b1);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    if (sink) l[r] += ex2f(0.f - (m[r] == -INFINITY ? 0.f : m[r]));
+    if (!valid[r]) continue;
+    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+    T* orow = out + (int64_t)(t0 + rr[r] / R) * ((int64_t)heads * vdim) + (g * R + hr[r]) * vdim;
+#pragma unroll
+    for (int nv = 0; nv < D / 8; ++nv) {
+      const int c = nv * 8 + tig * 2;
+      if (c < vdim) *reinterpret_cast<uint32_t*>(orow + c) = pack2<T>(o[nv][2 * r] * inv, o[nv][2 * r + 1] * inv);
+    }
+  }
+}
+
+template <typename T, int D>
+int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                         const int* cu_q, const int* ctx_len, const float* bias_table, const uint8_t* lut, int lut_n,
+                         int nbuckets, void* out, int nseq, int max_q, int heads, int kv_heads, int dim, int vdim,
+                         int block_size, int max_blocks, float scale, int sink, cudaStream_t st) {
+  const int R = heads / kv_heads;
+  const size_t smem = (size_t)2 * MMA_BN * (D + 8) * sizeof(T) + (size_t)nbuckets * R * sizeof(float);
+  auto kern = paged_bias_attention_mma_kernel<T, D>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid((max_q * R + MMA_BM - 1) / MMA_BM, kv_heads, nseq);
+  kern<<<grid, 128, smem, st>>>((const T*)q, ldq, (const T*)k_cache, (const T*)v_cache, block_tables, cu_q, ctx_len,
+                                bias_table, lut, lut_n, nbuckets, (T*)out, heads, kv_heads, dim, vdim, block_size,
+                                max_blocks, scale, sink);
+  return CB_LAUNCH_CHECK();
+}
+
 }  // namespace
 
 // ================================================================================================ C launchers
@@ -517,6 +727,29 @@ int cb_paged_bias_attention(const void* q, int64_t ldq, const void* k_cache, con
         (const T*)q, ldq, (const T*)k_cache, (const T*)v_cache, block_tables, token_seq, token_pos, bias_table,
         bucket_start, nbuckets, (T*)out, tokens, heads, kv_heads, dim, vdim, block_size, max_blocks, scale, sink);
   });
+  return CB_LAUNCH_CHECK();
+}
+
+// 16-bit dtypes, widths that are multiples of 8 and at most 128: the tensor-core kernel
+int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
+                                const int* block_tables, const int* cu_q, const int* ctx_len, const float* bias_table,
+                                const uint8_t* lut, int lut_n, int nbuckets, void* out, int nseq, int max_q, int heads,
+                                int kv_heads, int dim, int vdim, int block_size, int max_blocks, float scale, int sink,
+                                int dtype, cudaStream_t st) {
+  if (nseq == 0 || max_q == 0) return 0;
+  if (heads % kv_heads != 0 || dim % 8 != 0 || vdim % 8 != 0 || dim > 128 || vdim > 128 || (ldq & 1))
+    return (int)cudaErrorInvalidValue;
+  const int dmax = dim > vdim ? dim : vdim;
+#define CB_ATT_MMA(T, D)                                                                                              \
+  return launch_attention_mma<T, D>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, bias_table, lut, lut_n,   \
+                                    nbuckets, out, nseq, max_q, heads, kv_heads, dim, vdim, block_size, max_blocks,  \
+                                    scale, sink, st)
+  CB_DISPATCH_HALF(dtype, T, {
+    if (dmax <= 32) { CB_ATT_MMA(T, 32); }
+    else if (dmax <= 64) { CB_ATT_MMA(T, 64); }
+    else { CB_ATT_MMA(T, 128); }
+  });
+#undef CB_ATT_MMA
   return CB_LAUNCH_CHECK();
 }
 

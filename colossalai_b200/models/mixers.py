@@ -76,13 +76,15 @@ class BiasSinkAttention(_MixerBase):
             else:
                 v_other = first
                 lam = self._aux("lam", "cpu", lambda: self.v_mix.detach().float().cpu()).item()
-        table = starts = None
+        table = starts = lut = None
         if sp.bias_buckets:
             table = self._aux("rel", x.device, lambda: self.rel_bias.detach().float().contiguous())
             starts = self._aux("starts", x.device, lambda: torch.tensor(
                 mops.log_bucket_starts(sp.bias_buckets, sp.bias_max), dtype=torch.int32))
+            lut = self._aux("lut", x.device, lambda: mops.bucket_lut(
+                mops.log_bucket_starts(sp.bias_buckets, sp.bias_max)))
         o = kv_cache.attend_ragged(self.layer_idx, q, k, v, self.scale, bias_table=table, bucket_starts=starts,
-                                   sink=sp.sink, v_other=v_other, lam=lam)
+                                   sink=sp.sink, v_other=v_other, lam=lam, lut=lut)
         return self.o_proj(o)
 
 

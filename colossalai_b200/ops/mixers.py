@@ -21,7 +21,8 @@ from ._dispatch import use_native
 from ._dtypes import code
 
 __all__ = ["RaggedMeta", "short_conv_silu", "state_scan_decay", "state_scan_delta", "gated_group_rms_norm",
-           "rms_norm_residual", "rms_norm_f32in", "paged_kv_write_mix", "paged_bias_attention", "log_bucket_starts"]
+           "rms_norm_residual", "rms_norm_f32in", "paged_kv_write_mix", "paged_bias_attention", "log_bucket_starts",
+           "bucket_lut"]
 
 _lib = None
 
@@ -95,6 +96,16 @@ def log_bucket_starts(num_buckets: int, max_distance: float) -> List[int]:
             n += 1
         starts[b] = n
     return starts
+
+
+def bucket_lut(starts: Sequence[int]) -> torch.Tensor:
+    """distance -> bucket for every distance below the last bucket's first one (uint8; larger distances fall into the
+    last bucket), the form the tensor-core attention kernel reads."""
+    starts = [int(x) for x in starts]
+    lut = torch.zeros(max(starts[-1], 1), dtype=torch.uint8)
+    for b in range(len(starts) - 1):
+        lut[starts[b]: starts[b + 1]] = b
+    return lut
 
 
 # ------------------------------------------------------------------------------------------------ short convolution
@@ -302,11 +313,16 @@ def paged_kv_write_mix(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, 
 
 def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
                          meta: RaggedMeta, scale: float, bias_table: Optional[torch.Tensor] = None,
-                         bucket_starts: Optional[torch.Tensor] = None, sink: bool = False) -> torch.Tensor:
+                         bucket_starts: Optional[torch.Tensor] = None, sink: bool = False,
+                         lut: Optional[torch.Tensor] = None, tensor_cores: Optional[bool] = None) -> torch.Tensor:
     """Causal attention of every step token over positions 0..pos of its sequence in the paged cache.
     q [T, heads x dim]; caches [blocks, block_size, kv_heads, dim | vdim]; bias_table [buckets, heads] fp32 indexed by
     the bucket of the distance (`bucket_starts` [buckets] int32: smallest distance of each bucket); `sink` adds a key of
-    score 0 without a value to the softmax.  Returns [T, heads x vdim]."""
+    score 0 without a value to the softmax.  Returns [T, heads x vdim].
+
+    Two kernels: 16-bit inputs whose head widths are multiples of 8 up to 128 run on tensor cores (`lut` = `bucket_lut`
+    of the same buckets; built here when absent); everything else - fp32 above all - takes the exact CUDA-core kernel.
+    `tensor_cores` forces the choice."""
     T = q.shape[0]
     _, bs, G, dim = k_cache.shape
     vdim = v_cache.shape[3]
@@ -317,6 +333,24 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
             raise NotImplementedError("paged_bias_attention: value width above 256 is not supported")
         assert q.stride(1) == 1 and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
         out = torch.empty(T, heads * vdim, dtype=q.dtype, device=q.device)
+        mma_ok = (q.dtype in (torch.bfloat16, torch.float16) and dim % 8 == 0 and vdim % 8 == 0 and dim <= 128
+                  and vdim <= 128 and nb <= 255 and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0)
+        if tensor_cores is None:
+            tensor_cores = mma_ok
+        if tensor_cores:
+            if not mma_ok:
+                raise ValueError("paged_bias_attention: the tensor-core kernel needs 16-bit inputs and head widths "
+                                 "that are multiples of 8 up to 128")
+            if nb and lut is None:
+                lut = bucket_lut(bucket_starts.tolist()).to(q.device)
+            loader.check(_get_lib().cb_paged_bias_attention_mma(
+                loader.ptr(q), _i64(q.stride(0)), loader.ptr(k_cache), loader.ptr(v_cache), loader.ptr(block_tables),
+                loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len), loader.ptr(bias_table), loader.ptr(lut),
+                0 if lut is None else lut.numel(), nb, loader.ptr(out), meta.nseq, meta.max_q, heads, G, dim, vdim, bs,
+                block_tables.shape[1], _f(scale), int(sink), code(q.dtype), loader.stream_ptr()),
+                "paged_bias_attention_mma")
+            loader.launch_counter.add("paged_bias_attention_mma")
+            return out
         loader.check(_get_lib().cb_paged_bias_attention(
             loader.ptr(q), _i64(q.stride(0)), loader.ptr(k_cache), loader.ptr(v_cache), loader.ptr(block_tables),
             loader.ptr(meta.token_seq), loader.ptr(meta.token_pos), loader.ptr(bias_table), loader.ptr(bucket_starts), nb,

@@ -1,0 +1,223 @@
+"""Serving throughput of a hybrid decoder (Gopunex layers: channel-wise delta rule / bias+sink attention / lightning
+attention) beside a Llama of equal width, depth and head sizes, both with random weights through `LLMEngine`, plus the
+time of every mixer kernel alone against its roofline.
+
+    python examples/inference/benchmark_hybrid.py [--sizes 2048x8,4096x4] [--batch 8] [--in_len 2048] [--out_len 64]
+
+Also reachable as `python bench.py --workload hybrid-serve`.  One JSON line per (size, family) and one per kernel.
+Timing: CUDA events on the launching stream after warm-up; the kernel timings write a 256 MB buffer between runs (L2
+flush).  Rooflines use the measured copy bandwidth / bf16 GEMM throughput of MEASURED_PEAKS.json.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
+
+from colossalai_b200.inference import GenerationConfig, InferenceConfig  # noqa: E402
+from colossalai_b200.inference.core.llm_engine import LLMEngine  # noqa: E402
+from colossalai_b200.models import build_model  # noqa: E402
+from colossalai_b200.models.config import LayerSpec, MixerSpec, ModelConfig  # noqa: E402
+
+ROOT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..")
+
+
+def peaks():
+    try:
+        p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return p["hbm_gbs"] * 1e9, p["bf16_tflops"] * 1e12, "measured"
+    except Exception:
+        return 6.65e12, 1.59e15, "fallback"
+
+
+def hybrid_config(width: int, layers: int, vocab: int = 32000) -> ModelConfig:
+    H, d = width // 128, 128
+    att = MixerSpec(kind="attention", heads=H, kv_heads=max(H // 4, 1), dim=d, vdim=d, bias=True, scale=d ** -0.5,
+                    bias_buckets=32, bias_max=4096.0, sink=True, proj_norm=True, v_mix=True)
+    lig = MixerSpec(kind="lightning", heads=H, dim=d, vdim=d, decay=[1.0 - 2.0 ** -(5 + 3 * i / H) for i in range(H)])
+    dlt = MixerSpec(kind="channel_delta", heads=H, kv_heads=H, dim=d, vdim=d, conv=4, decay_rank=64, gate_rank=64)
+    order = [dlt, att, lig, dlt, att]
+    specs = [LayerSpec(mixer=order[i % len(order)], ff=4 * width) for i in range(layers)]
+    return ModelConfig(model_type="gopunex", vocab_size=vocab, hidden_size=width, intermediate_size=4 * width,
+                       layer_specs=specs, norm_eps=1e-5, hidden_act="relu2", glu=False, pos_type="none",
+                       norm_placement="sublayer_out", residual_mult=0.7, norm_weight_offset=1.0, fp32_residual=True,
+                       max_position_embeddings=1 << 20)
+
+
+def llama_config(width: int, layers: int, vocab: int = 32000) -> ModelConfig:
+    H = width // 128
+    # 8/3 x width gated feed-forward = the parameter count of the hybrid's 4 x width plain one
+    return ModelConfig(model_type="llama", vocab_size=vocab, hidden_size=width, intermediate_size=width * 8 // 3 // 64 * 64,
+                       num_hidden_layers=layers, num_attention_heads=H, num_key_value_heads=max(H // 4, 1), head_dim=128,
+                       max_position_embeddings=1 << 16)
+
+
+def build(cfg: ModelConfig):
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = build_model(cfg).to(torch.bfloat16)
+    with torch.no_grad():
+        for n, p in model.named_parameters():          # recurrent layers: non-degenerate convolutions and decays
+            if n.endswith("conv_weight"):
+                p.normal_(0, 0.5)
+            elif n.endswith("dt_bias") or n.endswith("rel_bias"):
+                p.normal_(0, 1.0)
+            elif n.endswith("v_mix"):
+                p.fill_(0.4)
+    return model.eval()
+
+
+def serve(cfg: ModelConfig, batch: int, in_len: int, out_len: int) -> dict:
+    model = build(cfg)
+    icfg = InferenceConfig(max_batch_size=batch, max_input_len=in_len, max_output_len=out_len, dtype="bf16",
+                           block_size=64, ignore_eos=True, max_num_batched_tokens=batch * in_len)
+    eng = LLMEngine(model, None, icfg)
+    gen = GenerationConfig(max_new_tokens=out_len)
+    eng.generation_config, eng.generation_config_dict = gen, gen.to_dict()
+    g = torch.Generator().manual_seed(1)
+    prompts = torch.randint(3, cfg.vocab_size, (batch, in_len), generator=g).tolist()
+
+    def run():
+        eng.add_request(prompts_token_ids=prompts, generation_config=gen)
+        torch.cuda.synchronize()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        eng.step()
+        e1.record()
+        steps = 0
+        while eng.request_handler.check_unfinished_reqs():
+            eng.step()
+            steps += 1
+        e2.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1), e1.elapsed_time(e2), steps
+
+    run()
+    run()
+    from colossalai_b200.kernel import loader
+
+    loader.launch_counter.reset()
+    tp, td, steps = run()
+    n_params = sum(p.numel() for p in model.parameters())
+    out = {"family": cfg.model_type, "width": cfg.hidden_size, "layers": cfg.num_hidden_layers, "params": n_params,
+           "batch": batch, "in_len": in_len, "out_len": out_len, "prefill_ms": tp,
+           "prefill_tokens_per_s": batch * in_len / (tp / 1e3), "decode_ms_per_step": td / max(steps, 1),
+           "decode_tokens_per_s": batch * steps / (td / 1e3), "our_kernel_launches": loader.launch_counter.count}
+    del eng, model
+    torch.cuda.empty_cache()
+    return out
+
+
+def _time(fn, flush, iters: int = 5) -> float:
+    for _ in range(3):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush.add_(1)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return sorted(ts)[len(ts) // 2]
+
+
+def kernels(width: int, batch: int, in_len: int) -> list:
+    """Every mixer kernel alone at one layer's sizes, prefill (batch x in_len tokens) and decode (batch tokens on
+    in_len of context), beside Llama's flash prefill and paged decode attention."""
+    from colossalai_b200 import ops
+    from colossalai_b200.ops import inference as iops
+    from colossalai_b200.ops import mixers as M
+
+    hbm, tflops, src = peaks()
+    dev, dt = "cuda", torch.bfloat16
+    H, d, G, bs = width // 128, 128, max(width // 128 // 4, 1), 64
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    rows = []
+
+    def rec(name, phase, ms, bytes_, flops, like=""):
+        ideal = max(bytes_ / hbm, flops / tflops) * 1e3
+        rows.append({"kernel": name, "phase": phase, "width": width, "ms": ms, "roofline_ms": ideal,
+                     "frac_of_" + src + "_roofline": ideal / ms, "bound": "hbm" if bytes_ / hbm > flops / tflops else "tensor",
+                     "like": like})
+
+    for phase, q_len, ctx in (("prefill", in_len, 0), ("decode", 1, in_len)):
+        T = batch * q_len
+        meta = M.RaggedMeta.build([q_len] * batch, [ctx] * batch, list(range(batch)), dev)
+        x = lambda c: torch.randn(T, c, device=dev, dtype=dt)
+        S = torch.zeros(batch, H, d, d, device=dev)
+        state_bytes = 2 * S.numel() * 4
+        q, k, v, a, b = x(H * d) * 0.1, x(H * d) * 0.1, x(H * d), x(H * d), x(H)
+        al, db = torch.zeros(H, device=dev), torch.zeros(H * d, device=dev)
+        ms = _time(lambda: M.state_scan_delta(q, k, v, a, b, al, db, S, meta, H, H, d, d), flush)
+        rec("state_scan_delta", phase, ms, T * (4 * H * d * 2 + H * d * 4) + state_bytes, 6.0 * T * H * d * d)
+        dec = torch.full((H,), 0.97, device=dev)
+        ms = _time(lambda: M.state_scan_decay(q, k, v, dec, S, meta, H, d, d), flush)
+        rec("state_scan_decay", phase, ms, T * (3 * H * d * 2 + H * d * 4) + state_bytes, 4.0 * T * H * d * d)
+        C = 3 * H * d
+        xc, w, st = x(C), torch.randn(C, 4, device=dev, dtype=dt), torch.zeros(batch, 3, C, device=dev, dtype=dt)
+        ms = _time(lambda: M.short_conv_silu(xc, w, st, meta), flush)
+        rec("short_conv_silu", phase, ms, 2 * T * C * 2, 0)
+        o, gate, wn = torch.randn(T, H * d, device=dev), x(H * d), torch.ones(d, device=dev, dtype=dt)
+        ms = _time(lambda: M.gated_group_rms_norm(o, wn, gate, d, 1e-5, dt), flush)
+        rec("gated_group_rmsnorm", phase, ms, T * H * d * (4 + 2 + 2), 0)
+        xs, y, wr = torch.randn(T, width, device=dev), x(width), torch.zeros(width, device=dev, dtype=dt)
+        ms = _time(lambda: M.rms_norm_residual(xs, y, wr, 1e-5, 0.7, 1.0), flush)
+        rec("rmsnorm_residual", phase, ms, T * width * (4 + 4 + 2 + 2), 0, like="rmsnorm_fwd(+residual)")
+        yl, wl = x(width), torch.ones(width, device=dev, dtype=dt)
+        ms = _time(lambda: ops.rms_norm(yl, wl, 1e-5, yl), flush)
+        rec("llama:rmsnorm_fwd(+residual)", phase, ms, T * width * 2 * 4, 0)
+        # attention over pages: ours (bias + sink, ragged) and Llama's (flash prefill / split-KV decode)
+        L = ctx + q_len
+        per = (L + bs - 1) // bs
+        kc = torch.randn(batch * per, bs, G, d, device=dev, dtype=dt)
+        vc = torch.randn(batch * per, bs, G, d, device=dev, dtype=dt)
+        tables = torch.arange(batch * per, dtype=torch.int32, device=dev).view(batch, per)
+        qa = x(H * d)
+        rel = torch.randn(32, H, device=dev)
+        starts = torch.tensor(M.log_bucket_starts(32, 4096.0), dtype=torch.int32, device=dev)
+        ms = _time(lambda: M.paged_bias_attention(qa, kc, vc, tables, meta, d ** -0.5, rel, starts, True), flush)
+        kv_bytes = 2 * batch * L * G * d * 2
+        att_flops = 4.0 * batch * H * d * (q_len * ctx + q_len * (q_len + 1) / 2)
+        rec("paged_bias_attention", phase, ms, kv_bytes + 2 * T * H * d * 2, att_flops,
+            like="flash prefill" if phase == "prefill" else "paged decode")
+        if phase == "prefill":
+            q3, k3, v3 = qa.view(T, H, d), x(G * d).view(T, G, d), x(G * d).view(T, G, d)
+            cu = torch.arange(0, T + 1, q_len, dtype=torch.int32, device=dev)
+            ms = _time(lambda: ops.attention(q3, k3, v3, causal=True, scale=d ** -0.5, cu_seqlens_q=cu, cu_seqlens_k=cu,
+                                             max_seqlen=q_len), flush)
+            rec("llama:flash_prefill_attention", phase, ms, kv_bytes + 2 * T * H * d * 2, att_flops)
+        else:
+            lens = torch.full((batch,), L, dtype=torch.int32, device=dev)
+            ms = _time(lambda: iops.paged_decode_attention(qa.view(T, H, d), kc, vc, tables, lens, d ** -0.5), flush)
+            rec("llama:paged_decode_attention", phase, ms, kv_bytes + 2 * T * H * d * 2, att_flops)
+    return rows
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sizes", default="2048x8,4096x4", help="width x layers, comma separated")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--in_len", type=int, default=2048)
+    ap.add_argument("--out_len", type=int, default=32)
+    ap.add_argument("--no-kernels", action="store_true")
+    ap.add_argument("--no-serve", action="store_true")
+    args = ap.parse_args(argv)
+    assert torch.cuda.is_available(), "this benchmark needs a GPU"
+    for size in args.sizes.split(","):
+        width, layers = (int(z) for z in size.split("x"))
+        if not args.no_serve:
+            for cfg in (hybrid_config(width, layers), llama_config(width, layers)):
+                print(json.dumps(serve(cfg, args.batch, args.in_len, args.out_len)), flush=True)
+        if not args.no_kernels:
+            for row in kernels(width, args.batch, args.in_len):
+                print(json.dumps(row), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -181,7 +181,8 @@ def _paged(L, G, d, dv, bs, dtype, dev, gen):
 
 @pytest.mark.parametrize("device", DEVICES)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,d,dv,bs", [(4, 2, 24, 16, 8), (6, 1, 48, 40, 16), (2, 2, 8, 130, 16), (3, 3, 20, 12, 32)])
+@pytest.mark.parametrize("H,G,d,dv,bs", [(4, 2, 24, 16, 8), (6, 1, 48, 40, 16), (2, 2, 8, 130, 16), (3, 3, 20, 12, 32),
+                                         (8, 2, 128, 128, 16), (4, 4, 64, 32, 64), (5, 1, 16, 72, 8)])
 def test_paged_bias_sink_attention(device, dtype, H, G, d, dv, bs):
     dev = _dev(device)
     g = torch.Generator().manual_seed(H + bs)
@@ -204,6 +205,28 @@ def test_paged_bias_sink_attention(device, dtype, H, G, d, dv, bs):
         M.paged_kv_write_mix(t(k), t(v), kc, vc, table.to(dev), meta, v_other=t(vo), lam=lam)
         outs.append(M.paged_bias_attention(t(q), kc, vc, table.to(dev), meta, 0.3, rel.to(dev), starts, sink=True))
     _close(torch.cat(outs), want, 2e-5 if dtype == torch.float32 else 3e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("sink,buckets", [(True, 10), (False, 10), (True, 0)])
+def test_tensor_core_and_exact_attention_kernels_agree(sink, buckets):
+    """A mixed step (portions of unequal length beside single tokens, unequal contexts) through both CUDA kernels."""
+    dev = _dev("cuda")
+    g = torch.Generator().manual_seed(5)
+    H, G, d, dv, bs = 8, 2, 48, 32, 16
+    q_lens, ctx = [70, 1, 5, 1, 130], [0, 200, 61, 0, 3]
+    n, T = len(q_lens), sum(q_lens)
+    per = max((c + l + bs - 1) // bs for c, l in zip(ctx, q_lens))
+    kc = torch.randn(n * per + 3, bs, G, d, generator=g).to(torch.bfloat16).to(dev)
+    vc = torch.randn(n * per + 3, bs, G, dv, generator=g).to(torch.bfloat16).to(dev)
+    tables = torch.randperm(n * per + 3, generator=g)[: n * per].int().view(n, per).to(dev)
+    q = torch.randn(T, H * d, generator=g).to(torch.bfloat16).to(dev)
+    meta = M.RaggedMeta.build(q_lens, ctx, list(range(n)), dev)
+    rel = torch.randn(buckets, H, generator=g).to(dev) if buckets else None
+    starts = torch.tensor(M.log_bucket_starts(buckets, 90), dtype=torch.int32, device=dev) if buckets else None
+    a = M.paged_bias_attention(q, kc, vc, tables, meta, 0.2, rel, starts, sink, tensor_cores=True)
+    b = M.paged_bias_attention(q, kc, vc, tables, meta, 0.2, rel, starts, sink, tensor_cores=False)
+    _close(a, b.cpu(), 2e-2)
 
 
 @pytest.mark.parametrize("device", DEVICES)
