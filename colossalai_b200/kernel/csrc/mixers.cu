@@ -12,7 +12,7 @@
 // depend on how the prompt was cut or on what else is in the batch.
 //
 //   cb_short_conv_silu      y = silu(causal depthwise conv(x)) over time, window of taps-1 inputs carried per slot
-//   cb_state_scan           S <- decay * S + k (x) v   (scalar decay per head), or the gated delta rule
+//   cb_state_scan           (prepare + scan) S <- decay * S + k (x) v   (scalar decay per head), or the gated delta rule
 //                           S <- g * S; u = beta (v - S^T k); S <- S + k (x) u  (decay per key channel); o = S^T q
 //   cb_gated_group_rmsnorm  out = o / rms_group(o) * w * sigmoid(gate)
 //   cb_rmsnorm_residual     x(fp32) += mult * y / rms(y) * (offset + w);  h = cast(x)
@@ -128,131 +128,227 @@ struct ScanParams {
   float unit_eps, q_scale;
 };
 
-template <int DK, int MODE, typename T>
-__global__ void __launch_bounds__(128) state_scan_kernel(ScanParams p) {
-  __shared__ __align__(16) float sq[SCAN_TOK_TILE][DK];
-  __shared__ __align__(16) float sk[SCAN_TOK_TILE][DK];
-  __shared__ __align__(16) float sg[MODE == SCAN_DELTA ? SCAN_TOK_TILE : 1][DK];
-  __shared__ float sbeta[SCAN_TOK_TILE];
-  const int vblocks = (p.vdim + blockDim.x - 1) / blockDim.x;
+// Two kernels.  `scan_prepare_kernel` is elementwise and fully parallel: activations, unit norms, decays and write
+// strengths of every token in fp32 into a workspace whose rows are padded to the kernel's key width (q, k: zeros;
+// decay: ones) and value rows to a multiple of SCAN_COLS.  `state_scan_kernel` is the recurrence: a CTA owns SCAN_COLS
+// value columns of one (sequence, head); column j of S lives in the registers of SCAN_PARTS adjacent lanes, each holding
+// DK / SCAN_PARTS of its rows, so S^T k and S^T q are partial sums per lane joined by two shuffles in a fixed order.
+// The workspace rows of SCAN_TOK_TILE tokens arrive by cp.async in a two-stage ring while the previous tile is walked.
+constexpr int SCAN_PARTS = 4;
+constexpr int SCAN_COLS = 32;          // 128 threads
+
+struct ScanWork {
+  float *q, *k, *g, *beta, *v;         // [T, qk_heads, DK] x2, [T, heads, DK], [T, heads], [T, heads, VP]
+  int DK, VP;
+};
+
+CB_DEVICE void cp_async16f(void* smem_dst, const void* gmem_src) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+
+template <int MODE, typename T>
+__global__ void __launch_bounds__(128) scan_prepare_kernel(ScanParams p, ScanWork w) {
+  const int64_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int dim = p.dim, vdim = p.vdim, DK = w.DK;
+  const T* q = (const T*)p.q + t * p.ldq;
+  const T* k = (const T*)p.k + t * p.ldk;
+  for (int hk = warp; hk < p.qk_heads; hk += nwarps) {
+    float* wq = w.q + (t * p.qk_heads + hk) * DK;
+    float* wk = w.k + (t * p.qk_heads + hk) * DK;
+    float ssq = 0.f, ssk = 0.f;
+    for (int i = lane; i < dim; i += 32) {
+      float qv = to_f32<T>(q[hk * dim + i]), kv = to_f32<T>(k[hk * dim + i]);
+      if (p.act_silu) { qv = silu_f(qv); kv = silu_f(kv); }
+      ssq = fmaf(qv, qv, ssq);
+      ssk = fmaf(kv, kv, ssk);
+      wq[i] = qv;
+      wk[i] = kv;
+    }
+    float rq = p.q_scale, rk = 1.f;
+    if (p.unit_qk) {
+      rq = p.q_scale / sqrtf(warp_sum(ssq) + p.unit_eps);
+      rk = 1.f / sqrtf(warp_sum(ssk) + p.unit_eps);
+    }
+    for (int i = lane; i < DK; i += 32) {      // a lane rescales what it wrote itself; the padding is zero
+      wq[i] = i < dim ? wq[i] * rq : 0.f;
+      wk[i] = i < dim ? wk[i] * rk : 0.f;
+    }
+  }
+  if (MODE == SCAN_DELTA) {
+    for (int h = warp; h < p.heads; h += nwarps) {
+      const float A = expf(p.a_log[h]);
+      for (int i = lane; i < DK; i += 32) {
+        float g = 1.f;
+        if (i < dim)
+          g = expf(-A * softplus_f(to_f32<T>(((const T*)p.araw)[t * p.lda + h * dim + i]) + p.dt_bias[h * dim + i]));
+        w.g[(t * p.heads + h) * DK + i] = g;
+      }
+    }
+    for (int h = threadIdx.x; h < p.heads; h += blockDim.x)
+      w.beta[t * p.heads + h] = sigmoid_f(to_f32<T>(((const T*)p.braw)[t * p.ldb + h]));
+  }
+  const T* v = (const T*)p.v + t * p.ldv;
+  for (int idx = threadIdx.x; idx < p.heads * w.VP; idx += blockDim.x) {
+    const int h = idx / w.VP, c = idx % w.VP;
+    float vv = c < vdim ? to_f32<T>(v[h * vdim + c]) : 0.f;
+    if (p.act_silu) vv = silu_f(vv);
+    w.v[t * p.heads * w.VP + idx] = vv;
+  }
+}
+
+template <int DK, int MODE>
+__global__ void __launch_bounds__(128, 3) state_scan_kernel(ScanParams p, ScanWork w) {
+  constexpr int RP = DK / SCAN_PARTS;  // rows per lane
+  constexpr int RPP = RP + 4;          // a lane's rows start 4 floats further: the four 16-byte reads of a warp hit
+  constexpr int DKP = SCAN_PARTS * RPP;  // different banks
+  constexpr int NROW = MODE == SCAN_DELTA ? 3 : 2;
+  constexpr int STAGE = SCAN_TOK_TILE * (NROW * DKP + SCAN_COLS + 4);     // floats per stage
+  extern __shared__ __align__(16) float scan_smem[];
+  const int vblocks = w.VP / SCAN_COLS;
   const int h = blockIdx.x / vblocks, vb = blockIdx.x % vblocks;
   const int s = blockIdx.y;
   const int t0 = p.cu_q[s], t1 = p.cu_q[s + 1];
   if (t0 >= t1) return;
-  const int j = vb * blockDim.x + threadIdx.x;
+  const int part = threadIdx.x % SCAN_PARTS;
+  const int col = threadIdx.x / SCAN_PARTS;
+  const int j = vb * SCAN_COLS + col;
   const bool active = j < p.vdim;
   const int hk = h / (p.heads / p.qk_heads);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int dim = p.dim, vdim = p.vdim;
+  const int r0 = part * RP, r0p = part * RPP;
   float* Sg = p.state + ((int64_t)p.slots[s] * p.heads + h) * dim * vdim;
-  float S[DK];
+  float S[RP];
   const bool carried = p.ctx_len[s] > 0;
 #pragma unroll
-  for (int i = 0; i < DK; ++i) S[i] = (carried && active && i < dim) ? Sg[(int64_t)i * vdim + j] : 0.f;
-  const T* q = (const T*)p.q;
-  const T* k = (const T*)p.k;
-  const T* v = (const T*)p.v;
+  for (int i = 0; i < RP; ++i) S[i] = (carried && active && r0 + i < dim) ? Sg[(int64_t)(r0 + i) * vdim + j] : 0.f;
   const float hd = MODE == SCAN_DECAY ? p.head_decay[h] : 0.f;
-  const float A = MODE == SCAN_DELTA ? expf(p.a_log[h]) : 0.f;
 
-  for (int tb = t0; tb < t1; tb += SCAN_TOK_TILE) {
+  auto load_tile = [&](int stage, int tb) {
+    float* base = scan_smem + stage * STAGE;
     const int nt = min(SCAN_TOK_TILE, t1 - tb);
-    __syncthreads();
-    for (int tt = warp; tt < nt; tt += nwarps) {
+    constexpr int CH = DK / 4;
+    for (int idx = threadIdx.x; idx < nt * CH; idx += blockDim.x) {
+      const int tt = idx / CH, c = (idx % CH) * 4;
+      const int dst = tt * DKP + c + 4 * (c / RP);
       const int64_t t = tb + tt;
-      float ssq = 0.f, ssk = 0.f;
-      for (int i = lane; i < DK; i += 32) {
-        float qv = 0.f, kv = 0.f;
-        if (i < dim) {
-          qv = to_f32<T>(q[t * p.ldq + hk * dim + i]);
-          kv = to_f32<T>(k[t * p.ldk + hk * dim + i]);
-          if (p.act_silu) { qv = silu_f(qv); kv = silu_f(kv); }
-        }
-        ssq = fmaf(qv, qv, ssq);
-        ssk = fmaf(kv, kv, ssk);
-        sq[tt][i] = qv;
-        sk[tt][i] = kv;
-        if (MODE == SCAN_DELTA) {
-          float g = 1.f;
-          if (i < dim) {
-            const float a = to_f32<T>(((const T*)p.araw)[t * p.lda + h * dim + i]) + p.dt_bias[h * dim + i];
-            g = expf(-A * softplus_f(a));
-          }
-          sg[tt][i] = g;
-        }
-      }
-      float rq = p.q_scale, rk = 1.f;
-      if (p.unit_qk) {
-        ssq = warp_sum(ssq);
-        ssk = warp_sum(ssk);
-        rq = p.q_scale / sqrtf(ssq + p.unit_eps);
-        rk = 1.f / sqrtf(ssk + p.unit_eps);
-      }
-      for (int i = lane; i < DK; i += 32) {   // a lane rescales what it wrote itself
-        sq[tt][i] *= rq;
-        sk[tt][i] *= rk;
-      }
-      if (MODE == SCAN_DELTA && lane == 0) sbeta[tt] = sigmoid_f(to_f32<T>(((const T*)p.braw)[t * p.ldb + h]));
+      cp_async16f(base + dst, w.q + (t * p.qk_heads + hk) * DK + c);
+      cp_async16f(base + SCAN_TOK_TILE * DKP + dst, w.k + (t * p.qk_heads + hk) * DK + c);
+      if (MODE == SCAN_DELTA) cp_async16f(base + 2 * SCAN_TOK_TILE * DKP + dst, w.g + (t * p.heads + h) * DK + c);
+    }
+    float* sv = base + NROW * SCAN_TOK_TILE * DKP;
+    for (int idx = threadIdx.x; idx < nt * (SCAN_COLS / 4); idx += blockDim.x) {
+      const int tt = idx / (SCAN_COLS / 4), c = (idx % (SCAN_COLS / 4)) * 4;
+      cp_async16f(sv + tt * SCAN_COLS + c, w.v + ((int64_t)(tb + tt) * p.heads + h) * w.VP + vb * SCAN_COLS + c);
+    }
+    if (MODE == SCAN_DELTA && threadIdx.x < nt)
+      sv[SCAN_TOK_TILE * SCAN_COLS + threadIdx.x] = w.beta[(int64_t)(tb + threadIdx.x) * p.heads + h];
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  load_tile(0, t0);
+  int stage = 0;
+  for (int tb = t0; tb < t1; tb += SCAN_TOK_TILE, stage ^= 1) {
+    const int nt = min(SCAN_TOK_TILE, t1 - tb);
+    if (tb + SCAN_TOK_TILE < t1) {              // the other stage was released by the barrier that ended the last pass
+      load_tile(stage ^ 1, tb + SCAN_TOK_TILE);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    if (!active) continue;
-    for (int tt = 0; tt < nt; ++tt) {
+    const float* sq = scan_smem + stage * STAGE;
+    const float* sk = sq + SCAN_TOK_TILE * DKP;
+    const float* sg = sk + SCAN_TOK_TILE * DKP;
+    const float* sv = sq + NROW * SCAN_TOK_TILE * DKP;
+    const float* sbeta = sv + SCAN_TOK_TILE * SCAN_COLS;
+    for (int tt = 0; tt < nt; ++tt) {            // every lane takes part in the shuffles, also for a padded column
       const int64_t t = tb + tt;
-      float vv = to_f32<T>(v[t * p.ldv + h * vdim + j]);
-      if (p.act_silu) vv = silu_f(vv);
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      const float vv = sv[tt * SCAN_COLS + col];
+      const float* kq = sk + tt * DKP + r0p;
+      const float* qq = sq + tt * DKP + r0p;
+      float o0 = 0.f, o1 = 0.f;
       if (MODE == SCAN_DELTA) {
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        const float* gq = sg + tt * DKP + r0p;
+        float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < DK; i += 4) {
-          const float4 g4 = *reinterpret_cast<const float4*>(&sg[tt][i]);
-          const float4 k4 = *reinterpret_cast<const float4*>(&sk[tt][i]);
+        for (int i = 0; i < RP; i += 4) {
+          const float4 g4 = *reinterpret_cast<const float4*>(gq + i);
+          const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
           S[i] *= g4.x; S[i + 1] *= g4.y; S[i + 2] *= g4.z; S[i + 3] *= g4.w;
           a0 = fmaf(S[i], k4.x, a0); a1 = fmaf(S[i + 1], k4.y, a1);
-          a2 = fmaf(S[i + 2], k4.z, a2); a3 = fmaf(S[i + 3], k4.w, a3);
+          a0 = fmaf(S[i + 2], k4.z, a0); a1 = fmaf(S[i + 3], k4.w, a1);
         }
-        const float u = sbeta[tt] * (vv - ((a0 + a1) + (a2 + a3)));
+        float kv = a0 + a1;
+        kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+        kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+        const float u = sbeta[tt] * (vv - kv);
 #pragma unroll
-        for (int i = 0; i < DK; i += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(&sk[tt][i]);
-          const float4 q4 = *reinterpret_cast<const float4*>(&sq[tt][i]);
+        for (int i = 0; i < RP; i += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
+          const float4 q4 = *reinterpret_cast<const float4*>(qq + i);
           S[i] = fmaf(k4.x, u, S[i]); S[i + 1] = fmaf(k4.y, u, S[i + 1]);
           S[i + 2] = fmaf(k4.z, u, S[i + 2]); S[i + 3] = fmaf(k4.w, u, S[i + 3]);
           o0 = fmaf(S[i], q4.x, o0); o1 = fmaf(S[i + 1], q4.y, o1);
-          o2 = fmaf(S[i + 2], q4.z, o2); o3 = fmaf(S[i + 3], q4.w, o3);
+          o0 = fmaf(S[i + 2], q4.z, o0); o1 = fmaf(S[i + 3], q4.w, o1);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < DK; i += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(&sk[tt][i]);
-          const float4 q4 = *reinterpret_cast<const float4*>(&sq[tt][i]);
+        for (int i = 0; i < RP; i += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
+          const float4 q4 = *reinterpret_cast<const float4*>(qq + i);
           S[i] = fmaf(hd, S[i], k4.x * vv); S[i + 1] = fmaf(hd, S[i + 1], k4.y * vv);
           S[i + 2] = fmaf(hd, S[i + 2], k4.z * vv); S[i + 3] = fmaf(hd, S[i + 3], k4.w * vv);
           o0 = fmaf(S[i], q4.x, o0); o1 = fmaf(S[i + 1], q4.y, o1);
-          o2 = fmaf(S[i + 2], q4.z, o2); o3 = fmaf(S[i + 3], q4.w, o3);
+          o0 = fmaf(S[i + 2], q4.z, o0); o1 = fmaf(S[i + 3], q4.w, o1);
         }
       }
-      p.out[t * ((int64_t)p.heads * vdim) + h * vdim + j] = (o0 + o1) + (o2 + o3);
+      float o = o0 + o1;
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (active && part == 0) p.out[t * ((int64_t)p.heads * vdim) + h * vdim + j] = o;
     }
+    __syncthreads();                            // this stage may be refilled in the next pass
   }
   if (active) {
 #pragma unroll
-    for (int i = 0; i < DK; ++i)
-      if (i < dim) Sg[(int64_t)i * vdim + j] = S[i];
+    for (int i = 0; i < RP; ++i)
+      if (r0 + i < dim) Sg[(int64_t)(r0 + i) * vdim + j] = S[i];
   }
 }
 
-template <int MODE, typename T> int launch_scan(const ScanParams& p, int nseq, cudaStream_t st) {
-  int threads = ((p.vdim + 31) / 32) * 32;
-  if (threads > 128) threads = 128;
-  const int vblocks = (p.vdim + threads - 1) / threads;
-  dim3 grid(p.heads * vblocks, nseq);
-  if (p.dim <= 16) state_scan_kernel<16, MODE, T><<<grid, threads, 0, st>>>(p);
-  else if (p.dim <= 32) state_scan_kernel<32, MODE, T><<<grid, threads, 0, st>>>(p);
-  else if (p.dim <= 64) state_scan_kernel<64, MODE, T><<<grid, threads, 0, st>>>(p);
-  else if (p.dim <= 128) state_scan_kernel<128, MODE, T><<<grid, threads, 0, st>>>(p);
-  else return (int)cudaErrorInvalidValue;
+template <int DK, int MODE> int launch_scan_dk(const ScanParams& p, const ScanWork& w, int nseq, cudaStream_t st) {
+  constexpr int DKP = SCAN_PARTS * (DK / SCAN_PARTS + 4);
+  constexpr int NROW = MODE == SCAN_DELTA ? 3 : 2;
+  const size_t smem = (size_t)2 * SCAN_TOK_TILE * (NROW * DKP + SCAN_COLS + 4) * sizeof(float);
+  auto kern = state_scan_kernel<DK, MODE>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid(p.heads * (w.VP / SCAN_COLS), nseq);
+  kern<<<grid, SCAN_COLS * SCAN_PARTS, smem, st>>>(p, w);
   return CB_LAUNCH_CHECK();
+}
+
+// workspace floats for `tokens` tokens: q, k rows, decay rows and write strengths (delta rule), value rows
+static inline int scan_dk(int dim) { return dim <= 16 ? 16 : dim <= 32 ? 32 : dim <= 64 ? 64 : 128; }
+static inline int scan_vp(int vdim) { return (vdim + SCAN_COLS - 1) / SCAN_COLS * SCAN_COLS; }
+
+template <int MODE, typename T>
+int launch_scan(const ScanParams& p, float* work, int64_t tokens, int nseq, cudaStream_t st) {
+  if (p.dim > 128) return (int)cudaErrorInvalidValue;
+  ScanWork w;
+  w.DK = scan_dk(p.dim);
+  w.VP = scan_vp(p.vdim);
+  w.q = work;
+  w.k = w.q + tokens * p.qk_heads * w.DK;
+  w.g = w.k + tokens * p.qk_heads * w.DK;
+  w.beta = w.g + (MODE == SCAN_DELTA ? tokens * p.heads * w.DK : 0);
+  w.v = w.beta + (MODE == SCAN_DELTA ? (tokens * p.heads + 3) / 4 * 4 : 0);
+  scan_prepare_kernel<MODE, T><<<(unsigned)tokens, 128, 0, st>>>(p, w);
+  if (w.DK == 16) return launch_scan_dk<16, MODE>(p, w, nseq, st);
+  if (w.DK == 32) return launch_scan_dk<32, MODE>(p, w, nseq, st);
+  if (w.DK == 64) return launch_scan_dk<64, MODE>(p, w, nseq, st);
+  return launch_scan_dk<128, MODE>(p, w, nseq, st);
 }
 
 // ------------------------------------------------------------------------------------------------ norms
@@ -459,26 +555,36 @@ CB_DEVICE void cp_async16(void* smem_dst, const void* gmem_src, uint32_t src_byt
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(src_bytes) : "memory");
 }
 
-template <typename T, int D>
-__global__ void __launch_bounds__(128) paged_bias_attention_mma_kernel(
+// Key range split (decode steps, few CTAs): with `chunk` > 0 grid.x also enumerates key chunks; a CTA then writes its
+// unnormalised partial (fp32 accumulator, running maximum, denominator without the sink) and `attention_merge_kernel`
+// joins the chunks of every (token, head) in ascending order.
+template <typename T, int D, int NW>
+__global__ void __launch_bounds__(NW * 32) paged_bias_attention_mma_kernel(
     const T* __restrict__ q, int64_t ldq, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const float* __restrict__ bias_table, const uint8_t* __restrict__ lut, int lut_n, int nbuckets, T* __restrict__ out,
-    int heads, int kv_heads, int dim, int vdim, int block_size, int max_blocks, float scale, int sink) {
+    int heads, int kv_heads, int dim, int vdim, int block_size, int max_blocks, float scale, int sink, int chunk,
+    int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+  constexpr int BM = NW * 16;
   constexpr int LDS = D + 8;                    // padded row: 16-byte aligned, conflict-free fragment reads
+  constexpr int TILE = MMA_BN * LDS;
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  T* Ks = reinterpret_cast<T*>(smem_raw);
-  T* Vs = Ks + MMA_BN * LDS;
-  float* tab = reinterpret_cast<float*>(Vs + MMA_BN * LDS);          // [nbuckets][R] of this kv head's group
+  T* KV = reinterpret_cast<T*>(smem_raw);       // [2 stages][K tile | V tile]
+  float* tab = reinterpret_cast<float*>(KV + 4 * TILE);             // [nbuckets][R] of this kv head's group
   const int s = blockIdx.z, g = blockIdx.y;
   const int R = heads / kv_heads;
   const int t0 = cu_q[s], qlen = cu_q[s + 1] - t0;
-  const int nrows = qlen * R, row0 = blockIdx.x * MMA_BM;
+  const int split = chunk > 0 ? blockIdx.x % max_splits : 0;
+  const int nrows = qlen * R, row0 = (chunk > 0 ? blockIdx.x / max_splits : blockIdx.x) * BM;
   if (row0 >= nrows) return;
   const int ctx = ctx_len[s];
+  const int last_row = min(nrows - 1, row0 + BM - 1);
+  const int key_lo = chunk > 0 ? split * chunk : 0;
+  const int pos_max = chunk > 0 ? min(ctx + last_row / R, key_lo + chunk - 1) : ctx + last_row / R;
+  if (key_lo > pos_max) return;                 // this chunk lies beyond every row of the tile
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
-  for (int i = tid; i < nbuckets * R; i += blockDim.x) tab[i] = bias_table[(i / R) * heads + g * R + (i % R)] * LOG2E;
+  for (int i = tid; i < nbuckets * R; i += NW * 32) tab[i] = bias_table[(i / R) * heads + g * R + (i % R)] * LOG2E;
   const int* bt = block_tables + (int64_t)s * max_blocks;
 
   int rr[2], pos[2], hr[2];
@@ -507,16 +613,18 @@ __global__ void __launch_bounds__(128) paged_bias_attention_mma_kernel(
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[nv][e] = 0.f;
   float m[2], l[2];
-  m[0] = m[1] = sink ? 0.f : -INFINITY;         // log2 domain (0 either way)
-  l[0] = l[1] = 0.f;                            // per-thread partial; the sink's 1 is added once at the end
+  m[0] = m[1] = (sink && chunk == 0) ? 0.f : -INFINITY;     // log2 domain; with chunks the sink joins in the merge
+  l[0] = l[1] = 0.f;                            // per-thread partial; the sink's share is added once at the end
   const float sc2 = scale * LOG2E;
-  const int last_row = min(nrows - 1, row0 + MMA_BM - 1);
-  const int pos_max = ctx + last_row / R;
+  // first / last position any row of this warp sees: tiles beyond are skipped, tiles before need no causal test
+  const int wlo = ctx + min(nrows - 1, row0 + warp * 16) / R;
+  const int whi = ctx + min(nrows - 1, row0 + warp * 16 + 15) / R;
 
-  for (int j0 = 0; j0 <= pos_max; j0 += MMA_BN) {
-    __syncthreads();                            // previous tile fully consumed (and `tab` visible on the first pass)
+  auto load_tile = [&](int stage, int j0) {
     constexpr int CH = D / 8;
-    for (int idx = tid; idx < MMA_BN * CH; idx += blockDim.x) {
+    T* Ks = KV + stage * 2 * TILE;
+    T* Vs = Ks + TILE;
+    for (int idx = tid; idx < MMA_BN * CH; idx += NW * 32) {
       const int r = idx / CH, c8 = (idx % CH) * 8;
       const int j = j0 + r;
       const bool in = j <= pos_max;
@@ -526,88 +634,133 @@ __global__ void __launch_bounds__(128) paged_bias_attention_mma_kernel(
       cp_async16(Vs + r * LDS + c8, v_cache + (vin ? row * vdim + c8 : 0), vin ? 16u : 0u);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  };
+
+  load_tile(0, key_lo);
+  int stage = 0;
+  for (int j0 = key_lo; j0 <= pos_max; j0 += MMA_BN, stage ^= 1) {
+    if (j0 + MMA_BN <= pos_max) {               // the other stage was released by the barrier that ended the last pass
+      load_tile(stage ^ 1, j0 + MMA_BN);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     __syncthreads();
-    const int wmax = ctx + min(nrows - 1, row0 + warp * 16 + 15) / R;     // last position any row of this warp sees
-    if (j0 > wmax) continue;                                              // warp-uniform: whole tile masked
-    float sacc[MMA_BN / 8][4];
+    if (j0 <= whi) {                            // warp-uniform: otherwise the whole tile is masked for this warp
+      const T* Ks = KV + stage * 2 * TILE;
+      const T* Vs = Ks + TILE;
+      float sacc[MMA_BN / 8][4];
 #pragma unroll
-    for (int nt = 0; nt < MMA_BN / 8; ++nt) {
+      for (int nt = 0; nt < MMA_BN / 8; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) sacc[nt][e] = 0.f;
+        for (int e = 0; e < 4; ++e) sacc[nt][e] = 0.f;
 #pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        const T* kp = Ks + (nt * 8 + gid) * LDS + ks * 16 + tig * 2;
-        mma_16816<T>(sacc[nt], qf[ks], *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
-      }
-    }
-    float mx[2] = {m[0], m[1]};
-#pragma unroll
-    for (int nt = 0; nt < MMA_BN / 8; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int r = e >> 1, j = j0 + nt * 8 + tig * 2 + (e & 1);
-        float sv = -INFINITY;
-        if (j <= pos[r]) {
-          sv = sacc[nt][e] * sc2;
-          if (nbuckets > 0) {
-            const int n = pos[r] - j;
-            const int b = n < lut_n ? (int)__ldg(lut + n) : nbuckets - 1;
-            sv += tab[b * R + hr[r]];
-          }
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const T* kp = Ks + (nt * 8 + gid) * LDS + ks * 16 + tig * 2;
+          mma_16816<T>(sacc[nt], qf[ks], *reinterpret_cast<const uint32_t*>(kp),
+                       *reinterpret_cast<const uint32_t*>(kp + 8));
         }
-        sacc[nt][e] = sv;
-        mx[r] = fmaxf(mx[r], sv);
       }
-    float alpha[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      const float mu = mx[r] == -INFINITY ? 0.f : mx[r];
-      alpha[r] = ex2f(m[r] - mu);                 // m = -inf -> 0
-      m[r] = mx[r];
-      l[r] *= alpha[r];
-      mx[r] = mu;
-    }
-#pragma unroll
-    for (int nv = 0; nv < D / 8; ++nv) {
-      o[nv][0] *= alpha[0]; o[nv][1] *= alpha[0];
-      o[nv][2] *= alpha[1]; o[nv][3] *= alpha[1];
-    }
-#pragma unroll
-    for (int nt = 0; nt < MMA_BN / 8; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float p = ex2f(sacc[nt][e] - mx[e >> 1]);
-        sacc[nt][e] = p;
-        l[e >> 1] += p;
+      const bool unmasked = j0 + MMA_BN - 1 <= wlo;
+      const bool far = nbuckets == 0 || wlo - (j0 + MMA_BN - 1) >= lut_n;     // every distance in the last bucket
+      float fb[2] = {0.f, 0.f};
+      if (nbuckets > 0) {
+        fb[0] = tab[(nbuckets - 1) * R + hr[0]];
+        fb[1] = tab[(nbuckets - 1) * R + hr[1]];
       }
+      float mx[2] = {m[0], m[1]};
+      if (unmasked && far) {
 #pragma unroll
-    for (int kk = 0; kk < MMA_BN / 16; ++kk) {
-      uint32_t pa[4];
-      pa[0] = pack2<T>(sacc[2 * kk][0], sacc[2 * kk][1]);
-      pa[1] = pack2<T>(sacc[2 * kk][2], sacc[2 * kk][3]);
-      pa[2] = pack2<T>(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
-      pa[3] = pack2<T>(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
-      const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(Vs + (kk * 16 + (lane & 15)) * LDS);
+        for (int nt = 0; nt < MMA_BN / 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float sv = fmaf(sacc[nt][e], sc2, fb[e >> 1]);
+            sacc[nt][e] = sv;
+            mx[e >> 1] = fmaxf(mx[e >> 1], sv);
+          }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < MMA_BN / 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1, j = j0 + nt * 8 + tig * 2 + (e & 1);
+            float sv = -INFINITY;
+            if (j <= pos[r]) {
+              sv = sacc[nt][e] * sc2;
+              if (nbuckets > 0) {
+                const int n = pos[r] - j;
+                sv += n < lut_n ? tab[(int)__ldg(lut + n) * R + hr[r]] : fb[r];
+              }
+            }
+            sacc[nt][e] = sv;
+            mx[r] = fmaxf(mx[r], sv);
+          }
+      }
+      float alpha[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float mu = mx[r] == -INFINITY ? 0.f : mx[r];
+        alpha[r] = ex2f(m[r] - mu);             // m = -inf -> 0
+        m[r] = mx[r];
+        l[r] *= alpha[r];
+        mx[r] = mu;
+      }
 #pragma unroll
       for (int nv = 0; nv < D / 8; ++nv) {
-        uint32_t b0, b1;
-        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
-                     : "=r"(b0), "=r"(b1) : "r"(vrow + nv * 16));
-        mma_16816<T>(o[nv], pa, b0, b1);
+        o[nv][0] *= alpha[0]; o[nv][1] *= alpha[0];
+        o[nv][2] *= alpha[1]; o[nv][3] *= alpha[1];
+      }
+#pragma unroll
+      for (int nt = 0; nt < MMA_BN / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pe = ex2f(sacc[nt][e] - mx[e >> 1]);
+          sacc[nt][e] = pe;
+          l[e >> 1] += pe;
+        }
+#pragma unroll
+      for (int kk = 0; kk < MMA_BN / 16; ++kk) {
+        uint32_t pa[4];
+        pa[0] = pack2<T>(sacc[2 * kk][0], sacc[2 * kk][1]);
+        pa[1] = pack2<T>(sacc[2 * kk][2], sacc[2 * kk][3]);
+        pa[2] = pack2<T>(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
+        pa[3] = pack2<T>(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+        const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(Vs + (kk * 16 + (lane & 15)) * LDS);
+#pragma unroll
+        for (int nv = 0; nv < D / 8; ++nv) {
+          uint32_t b0, b1;
+          asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                       : "=r"(b0), "=r"(b1) : "r"(vrow + nv * 16));
+          mma_16816<T>(o[nv], pa, b0, b1);
+        }
       }
     }
+    __syncthreads();                            // this stage may be refilled in the next pass
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-    if (sink) l[r] += ex2f(0.f - (m[r] == -INFINITY ? 0.f : m[r]));
     if (!valid[r]) continue;
+    const int64_t unit = (int64_t)(t0 + rr[r] / R) * heads + g * R + hr[r];
+    if (chunk > 0) {
+      float* po = part_o + (unit * max_splits + split) * vdim;
+      if (tig == 0) {
+        part_ml[(unit * max_splits + split) * 2] = m[r];
+        part_ml[(unit * max_splits + split) * 2 + 1] = l[r];
+      }
+#pragma unroll
+      for (int nv = 0; nv < D / 8; ++nv) {
+        const int c = nv * 8 + tig * 2;
+        if (c < vdim) *reinterpret_cast<float2*>(po + c) = make_float2(o[nv][2 * r], o[nv][2 * r + 1]);
+      }
+      continue;
+    }
+    if (sink) l[r] += ex2f(0.f - (m[r] == -INFINITY ? 0.f : m[r]));
     const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
-    T* orow = out + (int64_t)(t0 + rr[r] / R) * ((int64_t)heads * vdim) + (g * R + hr[r]) * vdim;
+    T* orow = out + unit * vdim;
 #pragma unroll
     for (int nv = 0; nv < D / 8; ++nv) {
       const int c = nv * 8 + tig * 2;
@@ -616,19 +769,62 @@ __global__ void __launch_bounds__(128) paged_bias_attention_mma_kernel(
   }
 }
 
-template <typename T, int D>
+// one warp per (token, head): joins the key chunks 0..pos / chunk in ascending order (log2-domain maxima)
+template <typename T>
+__global__ void __launch_bounds__(128) attention_merge_kernel(const float* __restrict__ part_o,
+                                                              const float* __restrict__ part_ml,
+                                                              const int* __restrict__ token_pos, T* __restrict__ out,
+                                                              int64_t tokens, int heads, int vdim, int chunk,
+                                                              int max_splits, int sink) {
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= tokens * heads) return;
+  const int nsp = token_pos[unit / heads] / chunk + 1;
+  float mm = sink ? 0.f : -INFINITY;
+  for (int sp = 0; sp < nsp; ++sp) mm = fmaxf(mm, part_ml[(unit * max_splits + sp) * 2]);
+  const float mu = mm == -INFINITY ? 0.f : mm;
+  float l = sink ? ex2f(0.f - mu) : 0.f;
+  float acc[ATT_MAX_VREG];
+#pragma unroll
+  for (int r = 0; r < ATT_MAX_VREG; ++r) acc[r] = 0.f;
+  for (int sp = 0; sp < nsp; ++sp) {
+    const float w = ex2f(part_ml[(unit * max_splits + sp) * 2] - mu);
+    l = fmaf(part_ml[(unit * max_splits + sp) * 2 + 1], w, l);
+    const float* po = part_o + (unit * max_splits + sp) * vdim;
+#pragma unroll
+    for (int r = 0; r < ATT_MAX_VREG; ++r) {
+      const int c = lane + 32 * r;
+      if (c < vdim) acc[r] = fmaf(po[c], w, acc[r]);
+    }
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int r = 0; r < ATT_MAX_VREG; ++r) {
+    const int c = lane + 32 * r;
+    if (c < vdim) out[unit * vdim + c] = from_f32<T>(acc[r] * inv);
+  }
+}
+
+template <typename T, int D, int NW>
 int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
-                         const int* cu_q, const int* ctx_len, const float* bias_table, const uint8_t* lut, int lut_n,
-                         int nbuckets, void* out, int nseq, int max_q, int heads, int kv_heads, int dim, int vdim,
-                         int block_size, int max_blocks, float scale, int sink, cudaStream_t st) {
+                         const int* cu_q, const int* ctx_len, const int* token_pos, const float* bias_table,
+                         const uint8_t* lut, int lut_n, int nbuckets, void* out, int64_t tokens, int nseq, int max_q,
+                         int heads, int kv_heads, int dim, int vdim, int block_size, int max_blocks, float scale, int sink,
+                         int chunk, int max_splits, float* part_o, float* part_ml, cudaStream_t st) {
   const int R = heads / kv_heads;
-  const size_t smem = (size_t)2 * MMA_BN * (D + 8) * sizeof(T) + (size_t)nbuckets * R * sizeof(float);
-  auto kern = paged_bias_attention_mma_kernel<T, D>;
+  const size_t smem = (size_t)4 * MMA_BN * (D + 8) * sizeof(T) + (size_t)nbuckets * R * sizeof(float);
+  auto kern = paged_bias_attention_mma_kernel<T, D, NW>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  dim3 grid((max_q * R + MMA_BM - 1) / MMA_BM, kv_heads, nseq);
-  kern<<<grid, 128, smem, st>>>((const T*)q, ldq, (const T*)k_cache, (const T*)v_cache, block_tables, cu_q, ctx_len,
-                                bias_table, lut, lut_n, nbuckets, (T*)out, heads, kv_heads, dim, vdim, block_size,
-                                max_blocks, scale, sink);
+  const int rowtiles = (max_q * R + NW * 16 - 1) / (NW * 16);
+  dim3 grid(rowtiles * (chunk > 0 ? max_splits : 1), kv_heads, nseq);
+  kern<<<grid, NW * 32, smem, st>>>((const T*)q, ldq, (const T*)k_cache, (const T*)v_cache, block_tables, cu_q, ctx_len,
+                                    bias_table, lut, lut_n, nbuckets, (T*)out, heads, kv_heads, dim, vdim, block_size,
+                                    max_blocks, scale, sink, chunk, max_splits, part_o, part_ml);
+  if (chunk > 0) {
+    const int64_t units = tokens * heads;
+    attention_merge_kernel<T><<<(unsigned)((units + 3) / 4), 128, 0, st>>>(part_o, part_ml, token_pos, (T*)out, tokens,
+                                                                          heads, vdim, chunk, max_splits, sink);
+  }
   return CB_LAUNCH_CHECK();
 }
 
@@ -653,18 +849,26 @@ int cb_short_conv_silu(const void* x, int64_t ldx, const void* w, void* state, v
   return CB_LAUNCH_CHECK();
 }
 
+// floats of workspace `cb_state_scan` needs for `tokens` tokens
+int64_t cb_state_scan_workspace(int mode, int64_t tokens, int heads, int qk_heads, int dim, int vdim) {
+  const int64_t DK = scan_dk(dim), VP = scan_vp(vdim);
+  int64_t n = 2 * tokens * qk_heads * DK + tokens * heads * VP;
+  if (mode == SCAN_DELTA) n += tokens * heads * DK + (tokens * heads + 3) / 4 * 4;
+  return n;
+}
+
 int cb_state_scan(int mode, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
                   const void* araw, int64_t lda, const void* braw, int64_t ldb, const float* head_decay,
-                  const float* a_log, const float* dt_bias, float* state, float* out, const int* cu_q,
-                  const int* ctx_len, const int* slots, int nseq, int heads, int qk_heads, int dim, int vdim,
-                  int act_silu, int unit_qk, float unit_eps, float q_scale, int dtype, cudaStream_t st) {
-  if (nseq == 0) return 0;
+                  const float* a_log, const float* dt_bias, float* state, float* out, float* work, int64_t tokens,
+                  const int* cu_q, const int* ctx_len, const int* slots, int nseq, int heads, int qk_heads, int dim,
+                  int vdim, int act_silu, int unit_qk, float unit_eps, float q_scale, int dtype, cudaStream_t st) {
+  if (nseq == 0 || tokens == 0) return 0;
   if (heads % qk_heads != 0) return (int)cudaErrorInvalidValue;
   ScanParams p{q, k, v, ldq, ldk, ldv, araw, lda, braw, ldb, head_decay, a_log, dt_bias, state, out, cu_q, ctx_len, slots,
                heads, qk_heads, dim, vdim, act_silu, unit_qk, unit_eps, q_scale};
   CB_DISPATCH_FLOAT(dtype, T, {
-    if (mode == SCAN_DELTA) return launch_scan<SCAN_DELTA, T>(p, nseq, st);
-    return launch_scan<SCAN_DECAY, T>(p, nseq, st);
+    if (mode == SCAN_DELTA) return launch_scan<SCAN_DELTA, T>(p, work, tokens, nseq, st);
+    return launch_scan<SCAN_DECAY, T>(p, work, tokens, nseq, st);
   });
   return CB_LAUNCH_CHECK();
 }
@@ -730,20 +934,28 @@ int cb_paged_bias_attention(const void* q, int64_t ldq, const void* k_cache, con
   return CB_LAUNCH_CHECK();
 }
 
-// 16-bit dtypes, widths that are multiples of 8 and at most 128: the tensor-core kernel
+// 16-bit dtypes, widths that are multiples of 8 and at most 128: the tensor-core kernel.  `chunk` > 0 (a multiple of 64)
+// splits the keys over CTAs; part_o [tokens x heads x max_splits x vdim] and part_ml [.. x 2] are its fp32 workspace.
 int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
-                                const int* block_tables, const int* cu_q, const int* ctx_len, const float* bias_table,
-                                const uint8_t* lut, int lut_n, int nbuckets, void* out, int nseq, int max_q, int heads,
-                                int kv_heads, int dim, int vdim, int block_size, int max_blocks, float scale, int sink,
-                                int dtype, cudaStream_t st) {
+                                const int* block_tables, const int* cu_q, const int* ctx_len, const int* token_pos,
+                                const float* bias_table, const uint8_t* lut, int lut_n, int nbuckets, void* out,
+                                int64_t tokens, int nseq, int max_q, int heads, int kv_heads, int dim, int vdim,
+                                int block_size, int max_blocks, float scale, int sink, int chunk, int max_splits,
+                                float* part_o, float* part_ml, int dtype, cudaStream_t st) {
   if (nseq == 0 || max_q == 0) return 0;
-  if (heads % kv_heads != 0 || dim % 8 != 0 || vdim % 8 != 0 || dim > 128 || vdim > 128 || (ldq & 1))
+  if (heads % kv_heads != 0 || dim % 8 != 0 || vdim % 8 != 0 || dim > 128 || vdim > 128 || (ldq & 1) ||
+      chunk % MMA_BN != 0)
     return (int)cudaErrorInvalidValue;
   const int dmax = dim > vdim ? dim : vdim;
+  const bool wide = max_q * (heads / kv_heads) > 64;      // 128 query rows per CTA once a portion fills them
 #define CB_ATT_MMA(T, D)                                                                                              \
-  return launch_attention_mma<T, D>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, bias_table, lut, lut_n,   \
-                                    nbuckets, out, nseq, max_q, heads, kv_heads, dim, vdim, block_size, max_blocks,  \
-                                    scale, sink, st)
+  if (wide)                                                                                                           \
+    return launch_attention_mma<T, D, 8>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table, \
+                                         lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,  \
+                                         block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, st); \
+  return launch_attention_mma<T, D, 4>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table,  \
+                                       lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,   \
+                                       block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, st)
   CB_DISPATCH_HALF(dtype, T, {
     if (dmax <= 32) { CB_ATT_MMA(T, 32); }
     else if (dmax <= 64) { CB_ATT_MMA(T, 64); }

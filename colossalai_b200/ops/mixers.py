@@ -25,6 +25,7 @@ __all__ = ["RaggedMeta", "short_conv_silu", "state_scan_decay", "state_scan_delt
            "bucket_lut"]
 
 _lib = None
+_SPLIT_BELOW_TILES = 148        # attention steps with fewer CTAs than SMs split their keys
 
 
 def _get_lib():
@@ -150,13 +151,18 @@ def _scan_native(mode, q, k, v, araw, braw, head_decay, a_log, dt_bias, state, m
         assert t.stride(1) == 1
     assert state.dtype == torch.float32 and state.is_contiguous()
     ld = lambda t: _i64(0 if t is None else t.stride(0))
-    loader.check(_get_lib().cb_state_scan(
+    lib = _get_lib()
+    lib.cb_state_scan_workspace.restype = ctypes.c_int64
+    # fp32 rows the elementwise prepare kernel writes and the recurrence streams through shared memory
+    work = torch.empty(lib.cb_state_scan_workspace(mode, _i64(T), heads, qk_heads, dim, vdim), dtype=torch.float32,
+                       device=q.device)
+    loader.check(lib.cb_state_scan(
         mode, loader.ptr(q), ld(q), loader.ptr(k), ld(k), loader.ptr(v), ld(v), loader.ptr(araw), ld(araw),
         loader.ptr(braw), ld(braw), loader.ptr(head_decay), loader.ptr(a_log), loader.ptr(dt_bias), loader.ptr(state),
-        loader.ptr(out), loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len), loader.ptr(meta.slots), meta.nseq, heads,
-        qk_heads, dim, vdim, int(act_silu), int(unit_qk), _f(unit_eps), _f(q_scale), code(q.dtype),
-        loader.stream_ptr()), "state_scan")
-    loader.launch_counter.add("state_scan")
+        loader.ptr(out), loader.ptr(work), _i64(T), loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len),
+        loader.ptr(meta.slots), meta.nseq, heads, qk_heads, dim, vdim, int(act_silu), int(unit_qk), _f(unit_eps),
+        _f(q_scale), code(q.dtype), loader.stream_ptr()), "state_scan")
+    loader.launch_counter.add("state_scan", 2)
     return out
 
 
@@ -343,11 +349,26 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                                  "that are multiples of 8 up to 128")
             if nb and lut is None:
                 lut = bucket_lut(bucket_starts.tolist()).to(q.device)
+            # few CTAs (decode steps): split the keys so that about two waves of CTAs run, join the parts afterwards
+            R = heads // G
+            tiles = meta.nseq * G * ((meta.max_q * R + 63) // 64)
+            max_len = max(c + n for c, n in zip(meta.ctx_lens, meta.q_lens))
+            chunk = splits = 0
+            part_o = part_ml = None
+            if tiles < _SPLIT_BELOW_TILES and max_len >= 256:
+                chunk = max(128, -(-(max_len * tiles // (2 * _SPLIT_BELOW_TILES)) // 64) * 64)
+                splits = -(-max_len // chunk)
+                if splits > 1:
+                    part_o = torch.empty(T * heads * splits * vdim, dtype=torch.float32, device=q.device)
+                    part_ml = torch.empty(T * heads * splits * 2, dtype=torch.float32, device=q.device)
+                else:
+                    chunk = splits = 0
             loader.check(_get_lib().cb_paged_bias_attention_mma(
                 loader.ptr(q), _i64(q.stride(0)), loader.ptr(k_cache), loader.ptr(v_cache), loader.ptr(block_tables),
-                loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len), loader.ptr(bias_table), loader.ptr(lut),
-                0 if lut is None else lut.numel(), nb, loader.ptr(out), meta.nseq, meta.max_q, heads, G, dim, vdim, bs,
-                block_tables.shape[1], _f(scale), int(sink), code(q.dtype), loader.stream_ptr()),
+                loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len), loader.ptr(meta.token_pos), loader.ptr(bias_table),
+                loader.ptr(lut), 0 if lut is None else lut.numel(), nb, loader.ptr(out), _i64(T), meta.nseq, meta.max_q,
+                heads, G, dim, vdim, bs, block_tables.shape[1], _f(scale), int(sink), chunk, splits,
+                loader.ptr(part_o), loader.ptr(part_ml), code(q.dtype), loader.stream_ptr()),
                 "paged_bias_attention_mma")
             loader.launch_counter.add("paged_bias_attention_mma")
             return out

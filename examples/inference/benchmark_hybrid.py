@@ -36,7 +36,7 @@ def peaks():
 def hybrid_config(width: int, layers: int, vocab: int = 32000) -> ModelConfig:
     H, d = width // 128, 128
     att = MixerSpec(kind="attention", heads=H, kv_heads=max(H // 4, 1), dim=d, vdim=d, bias=True, scale=d ** -0.5,
-                    bias_buckets=32, bias_max=4096.0, sink=True, proj_norm=True, v_mix=True)
+                    bias_buckets=32, bias_max=512.0, sink=True, proj_norm=True, v_mix=True)
     lig = MixerSpec(kind="lightning", heads=H, dim=d, vdim=d, decay=[1.0 - 2.0 ** -(5 + 3 * i / H) for i in range(H)])
     dlt = MixerSpec(kind="channel_delta", heads=H, kv_heads=H, dim=d, vdim=d, conv=4, decay_rank=64, gate_rank=64)
     order = [dlt, att, lig, dlt, att]
@@ -180,7 +180,7 @@ def kernels(width: int, batch: int, in_len: int) -> list:
         tables = torch.arange(batch * per, dtype=torch.int32, device=dev).view(batch, per)
         qa = x(H * d)
         rel = torch.randn(32, H, device=dev)
-        starts = torch.tensor(M.log_bucket_starts(32, 4096.0), dtype=torch.int32, device=dev)
+        starts = torch.tensor(M.log_bucket_starts(32, 512.0), dtype=torch.int32, device=dev)
         ms = _time(lambda: M.paged_bias_attention(qa, kc, vc, tables, meta, d ** -0.5, rel, starts, True), flush)
         kv_bytes = 2 * batch * L * G * d * 2
         att_flops = 4.0 * batch * H * d * (q_len * ctx + q_len * (q_len + 1) / 2)

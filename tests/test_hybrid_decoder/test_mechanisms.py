@@ -209,12 +209,14 @@ def test_paged_bias_sink_attention(device, dtype, H, G, d, dv, bs):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("sink,buckets", [(True, 10), (False, 10), (True, 0)])
-def test_tensor_core_and_exact_attention_kernels_agree(sink, buckets):
-    """A mixed step (portions of unequal length beside single tokens, unequal contexts) through both CUDA kernels."""
+@pytest.mark.parametrize("q_lens,ctx", [([70, 1, 5, 1, 130], [0, 200, 61, 0, 3]),      # portions beside single tokens
+                                        ([1, 1, 3], [700, 0, 300]),                    # few rows, long contexts: split keys
+                                        ([300], [129])])                               # 128-row tiles, context + portion
+def test_tensor_core_and_exact_attention_kernels_agree(sink, buckets, q_lens, ctx):
+    """Mixed steps through both CUDA kernels: the tensor-core one (also with its keys split over CTAs) and the exact one."""
     dev = _dev("cuda")
     g = torch.Generator().manual_seed(5)
     H, G, d, dv, bs = 8, 2, 48, 32, 16
-    q_lens, ctx = [70, 1, 5, 1, 130], [0, 200, 61, 0, 3]
     n, T = len(q_lens), sum(q_lens)
     per = max((c + l + bs - 1) // bs for c, l in zip(ctx, q_lens))
     kc = torch.randn(n * per + 3, bs, G, d, generator=g).to(torch.bfloat16).to(dev)
