@@ -25,10 +25,13 @@ CB_DEVICE float gelu_erf_grad_f(float x) {
 }
 
 // act: 0 = silu, 1 = gelu(tanh), 2 = gelu(erf)
+// ACT: 0 silu, 1 gelu (tanh), 2 gelu (erf), 3 squared relu
 template <int ACT> CB_DEVICE float act_f(float x) {
+  if (ACT == 3) { const float r = fmaxf(x, 0.f); return r * r; }
   return ACT == 0 ? silu_f(x) : (ACT == 1 ? gelu_tanh_f(x) : gelu_erf_f(x));
 }
 template <int ACT> CB_DEVICE float act_grad_f(float x) {
+  if (ACT == 3) return 2.f * fmaxf(x, 0.f);
   if (ACT == 0) { const float s = sigmoid_f(x); return s * (1.f + x * (1.f - s)); }
   return ACT == 1 ? gelu_tanh_grad_f(x) : gelu_erf_grad_f(x);
 }
@@ -251,6 +254,7 @@ int cb_bias_act_fwd(const void* x, const void* bias, void* y, int64_t rows, int 
     const int g = ew_grid(rows * (H / Vec16<T>::N), 256);
     if (act == 0) bias_act_fwd_kernel<T, 0><<<g, 256, 0, s>>>((const T*)x, (const T*)bias, (T*)y, rows, H);
     else if (act == 1) bias_act_fwd_kernel<T, 1><<<g, 256, 0, s>>>((const T*)x, (const T*)bias, (T*)y, rows, H);
+    else if (act == 3) bias_act_fwd_kernel<T, 3><<<g, 256, 0, s>>>((const T*)x, (const T*)bias, (T*)y, rows, H);
     else bias_act_fwd_kernel<T, 2><<<g, 256, 0, s>>>((const T*)x, (const T*)bias, (T*)y, rows, H);
   });
   return CB_LAUNCH_CHECK();
@@ -263,6 +267,7 @@ int cb_bias_act_bwd(const void* dy, const void* x, const void* bias, void* dx, i
     const int g = ew_grid(rows * (H / Vec16<T>::N), 256);
     if (act == 0) bias_act_bwd_kernel<T, 0><<<g, 256, 0, s>>>((const T*)dy, (const T*)x, (const T*)bias, (T*)dx, rows, H);
     else if (act == 1) bias_act_bwd_kernel<T, 1><<<g, 256, 0, s>>>((const T*)dy, (const T*)x, (const T*)bias, (T*)dx, rows, H);
+    else if (act == 3) bias_act_bwd_kernel<T, 3><<<g, 256, 0, s>>>((const T*)dy, (const T*)x, (const T*)bias, (T*)dx, rows, H);
     else bias_act_bwd_kernel<T, 2><<<g, 256, 0, s>>>((const T*)dy, (const T*)x, (const T*)bias, (T*)dx, rows, H);
   });
   return CB_LAUNCH_CHECK();

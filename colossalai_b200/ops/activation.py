@@ -15,7 +15,8 @@ from ..kernel import loader
 from ._dispatch import use_native
 from ._dtypes import code
 
-_ACT = {"silu": 0, "swiglu": 0, "gelu_tanh": 1, "gelu_new": 1, "gelu_pytorch_tanh": 1, "gelu": 2, "geglu": 2}
+_ACT = {"silu": 0, "swiglu": 0, "gelu_tanh": 1, "gelu_new": 1, "gelu_pytorch_tanh": 1, "gelu": 2, "geglu": 2,
+        "relu2": 3, "relu_squared": 3}
 _lib = None
 
 
@@ -31,6 +32,8 @@ def _act_ref(x: torch.Tensor, act: int) -> torch.Tensor:
         return F.silu(x)
     if act == 1:
         return F.gelu(x, approximate="tanh")
+    if act == 3:
+        return F.relu(x).square()
     return F.gelu(x)
 
 
@@ -137,7 +140,7 @@ def get_activation(name: str):
     if name == "relu":
         return F.relu
     if name in ("relu2", "relu_squared"):
-        return lambda x: F.relu(x).square()
+        return lambda x: bias_act(x, None, "relu2")          # one fused kernel on CUDA tensors
     if name == "quick_gelu":
         return lambda x: x * torch.sigmoid(1.702 * x)
     raise ValueError(f"unknown activation {name}")

@@ -32,7 +32,21 @@ def _get_lib():
     global _lib
     if _lib is None:
         _lib = loader.load("cb200_mixers")
+        _lib.cb_state_scan_workspace.restype = ctypes.c_int64
     return _lib
+
+
+_workspaces = {}
+
+
+def _workspace(name: str, numel: int, device) -> torch.Tensor:
+    """Grow-only fp32 scratch per (purpose, device): consecutive layers run on one stream, so they can share it."""
+    key = (name, str(device))
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < numel:
+        buf = torch.empty(max(int(numel), 1), dtype=torch.float32, device=device)
+        _workspaces[key] = buf
+    return buf
 
 
 def _i64(v: int) -> ctypes.c_int64:
@@ -152,10 +166,8 @@ def _scan_native(mode, q, k, v, araw, braw, head_decay, a_log, dt_bias, state, m
     assert state.dtype == torch.float32 and state.is_contiguous()
     ld = lambda t: _i64(0 if t is None else t.stride(0))
     lib = _get_lib()
-    lib.cb_state_scan_workspace.restype = ctypes.c_int64
     # fp32 rows the elementwise prepare kernel writes and the recurrence streams through shared memory
-    work = torch.empty(lib.cb_state_scan_workspace(mode, _i64(T), heads, qk_heads, dim, vdim), dtype=torch.float32,
-                       device=q.device)
+    work = _workspace("scan", lib.cb_state_scan_workspace(mode, _i64(T), heads, qk_heads, dim, vdim), q.device)
     loader.check(lib.cb_state_scan(
         mode, loader.ptr(q), ld(q), loader.ptr(k), ld(k), loader.ptr(v), ld(v), loader.ptr(araw), ld(araw),
         loader.ptr(braw), ld(braw), loader.ptr(head_decay), loader.ptr(a_log), loader.ptr(dt_bias), loader.ptr(state),
@@ -359,8 +371,8 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                 chunk = max(128, -(-(max_len * tiles // (2 * _SPLIT_BELOW_TILES)) // 64) * 64)
                 splits = -(-max_len // chunk)
                 if splits > 1:
-                    part_o = torch.empty(T * heads * splits * vdim, dtype=torch.float32, device=q.device)
-                    part_ml = torch.empty(T * heads * splits * 2, dtype=torch.float32, device=q.device)
+                    part_o = _workspace("attn_o", T * heads * splits * vdim, q.device)
+                    part_ml = _workspace("attn_ml", T * heads * splits * 2, q.device)
                 else:
                     chunk = splits = 0
             loader.check(_get_lib().cb_paged_bias_attention_mma(
