@@ -85,6 +85,7 @@ class LLMEngine(BaseEngine):
         self.counter = count()
         self.use_cuda_graph = self.inference_config.use_cuda_graph and torch.cuda.is_available() \
             and not self.ragged_mode
+        self.ragged_graphs: Dict[int, CUDAGraphRunner] = {}
         if self.use_cuda_graph and (self.model_config.head_dim not in (64, 128, 256)
                                     or self.dtype not in (torch.float16, torch.bfloat16)):
             # the decode step must stay on the native paged kernel to be capturable (the reference path syncs)
@@ -101,6 +102,8 @@ class LLMEngine(BaseEngine):
         self._verify_args()
         if self.use_cuda_graph:
             self.capture_model()
+        elif self.ragged_mode and self.inference_config.use_cuda_graph and torch.cuda.is_available():
+            self.capture_ragged_decode()
 
     # ------------------------------------------------------------------ model
     def init_model(self, model_or_path, model_policy=None, model_shard_infer_config=None) -> None:
@@ -377,6 +380,34 @@ class LLMEngine(BaseEngine):
 
     # ------------------------------------------------------------------ ragged steps
     @torch.inference_mode()
+    def capture_ragged_decode(self) -> None:
+        """CUDA graphs of the ragged step for pure decode batches (one token per sequence), one per batch size.  The
+        step's layout lives in one fixed int32 buffer that a replay refills; launch shapes (attention key chunks) are
+        those of the longest context the page table can hold, kernels leave early where a sequence is shorter."""
+        from ...models.transformer import SeqMeta
+
+        rt = self.kv_runtime
+        max_blocks = self.request_handler.cache_manager.get_max_blocks_per_sequence()
+        max_ctx = max_blocks * self.inference_config.block_size - 1
+        for bs in reversed([b for b in _BATCH_SIZES_TO_CAPTURE if b <= self.inference_config.max_batch_size]):
+            def fn(input_ids, layout, block_tables, bs=bs):
+                positions = rt.set_ragged_static(layout, block_tables, bs, max_ctx)
+                meta = SeqMeta(batch=1, seqlen=bs, positions=positions)
+                out = self.model(input_ids=input_ids.view(1, -1), kv_cache=rt, meta=meta)
+                return out["logits"][:, : self.model_config.vocab_size].float()
+
+            from ...ops.mixers import RaggedMeta
+
+            runner = CUDAGraphRunner(fn)
+            layout = torch.tensor(RaggedMeta.flat_list([1] * bs, [1] * bs, list(range(bs))), dtype=torch.int32,
+                                  device=self.device)
+            runner.capture(memory_pool=self.graph_memory_pool,
+                           input_ids=torch.zeros(bs, dtype=torch.long, device=self.device), layout=layout,
+                           block_tables=torch.zeros(bs, max_blocks, dtype=torch.int32, device=self.device))
+            self.graph_memory_pool = runner.graph.pool()
+            self.ragged_graphs[bs] = runner
+
+    @torch.inference_mode()
     def forward_ragged(self, entries, want: Optional[List[List[int]]] = None) -> torch.Tensor:
         """The step function of ragged mode.  `entries`: [(RaggedSeq, next tokens)], all run as one batch - portions of
         prompts beside single decoded tokens - from the cache and state that earlier steps left.  `want[i]`: places
@@ -399,6 +430,16 @@ class LLMEngine(BaseEngine):
             return torch.empty(0, self.model_config.vocab_size, dtype=torch.float32, device=self.device)
         input_ids = torch.tensor(flat, dtype=torch.long).to(self.device, non_blocking=True)
         tables = torch.stack([rs.block_table for rs, _ in entries])
+        runner = self.ragged_graphs.get(len(entries))
+        if runner is not None and all(n == 1 for n in q_lens) and rows == list(range(len(entries))):
+            from ...ops.mixers import RaggedMeta
+
+            layout = torch.tensor(RaggedMeta.flat_list(q_lens, [rs.ctx_len for rs, _ in entries],
+                                                       [rs.slot for rs, _ in entries]), dtype=torch.int32)
+            logits = runner(input_ids=input_ids, layout=layout, block_tables=tables).clone()
+            for rs, _ in entries:
+                rs.ctx_len += 1
+            return logits
         positions = self.kv_runtime.set_ragged_step(tables, q_lens, [rs.ctx_len for rs, _ in entries],
                                                     [rs.slot for rs, _ in entries], self.device)
         from ...models.transformer import SeqMeta

@@ -74,6 +74,19 @@ class PagedKVRuntime:
         self.shared = {}
         return self.token_pos.long()
 
+    def set_ragged_static(self, flat: torch.Tensor, block_tables: torch.Tensor, nseq: int, max_ctx: int) -> torch.Tensor:
+        """Decode step over fixed device buffers (what a CUDA graph of the step captures and replays)."""
+        from ...ops.mixers import RaggedMeta
+
+        self.ragged = RaggedMeta.decode_static(flat, nseq, max_ctx)
+        self.block_tables = block_tables
+        self.token_seq, self.token_pos = self.ragged.token_seq, self.ragged.token_pos
+        self.seq_lens = self.ragged.ctx_len + 1
+        self.is_prompt, self.q_per_seq, self.cu_seqlens = False, 1, None
+        self.max_len_host = max_ctx + 1
+        self.shared = {}
+        return self.token_pos.long()
+
     def layer_state(self, layer_idx: int) -> dict:
         return self.states[layer_idx]
 

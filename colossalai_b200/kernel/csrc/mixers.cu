@@ -30,6 +30,11 @@ CB_DEVICE float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 CB_DEVICE float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 // ------------------------------------------------------------------------------------------------ short convolution
+// The convolution's activation is stored in the compute dtype: for 16-bit outputs the hardware exponential and
+// reciprocal (relative error ~1e-6) are far inside the rounding of the store; fp32 keeps the IEEE forms.
+template <typename T> CB_DEVICE float conv_silu(float x) { return x * __frcp_rn(1.f + __expf(-x)); }
+template <> CB_DEVICE float conv_silu<float>(float x) { return silu_f(x); }
+
 constexpr int CONV_MAX_TAPS = 8;
 constexpr int CONV_TOK_TILE = 32;
 
@@ -68,12 +73,74 @@ __global__ void __launch_bounds__(128) short_conv_silu_kernel(const T* __restric
 #pragma unroll
     for (int i = 0; i < CONV_MAX_TAPS; ++i)
       if (i == taps - 1) acc = fmaf(wt[i], cur, acc);
-    out[(int64_t)(t0 + j) * ldo + c] = from_f32<T>(apply_silu ? silu_f(acc) : acc);
+    out[(int64_t)(t0 + j) * ldo + c] = from_f32<T>(apply_silu ? conv_silu<T>(acc) : acc);
 #pragma unroll
     for (int i = 0; i < CONV_MAX_TAPS - 1; ++i) {
       if (i < taps - 2) win[i] = win[i + 1];
       else if (i == taps - 2) win[i] = cur;
     }
+  }
+}
+
+// 16 bytes of adjacent channels per thread (8 x 16-bit or 4 x fp32) for up to 4 taps: the row segment a warp touches is
+// 512 bytes instead of 64.  Needs channel count, row strides and base addresses that are multiples of the vector.
+constexpr int CONV_VEC_TAPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(128) short_conv_silu_vec_kernel(const T* __restrict__ x, int64_t ldx,
+                                                                  const T* __restrict__ w, const T* __restrict__ state,
+                                                                  T* __restrict__ out, int64_t ldo,
+                                                                  const int* __restrict__ cu_q,
+                                                                  const int* __restrict__ ctx_len,
+                                                                  const int* __restrict__ slots, int C, int taps,
+                                                                  int apply_silu) {
+  constexpr int V = Vec16<T>::N;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+  const int s = blockIdx.z;
+  const int t0 = cu_q[s], qlen = cu_q[s + 1] - t0;
+  const int j0 = blockIdx.y * CONV_TOK_TILE;
+  if (c >= C || j0 >= qlen) return;
+  const bool carried = ctx_len[s] > 0;
+  const T* st = state + (int64_t)slots[s] * (taps - 1) * C;
+  float wt[CONV_VEC_TAPS][V], win[CONV_VEC_TAPS - 1][V];
+#pragma unroll
+  for (int e = 0; e < V; ++e)
+#pragma unroll
+    for (int i = 0; i < CONV_VEC_TAPS; ++i) wt[i][e] = i < taps ? to_f32<T>(w[(int64_t)(c + e) * taps + i]) : 0.f;
+#pragma unroll
+  for (int i = 0; i < CONV_VEC_TAPS - 1; ++i) {
+    Vec16<T> v;
+    v.raw = make_uint4(0u, 0u, 0u, 0u);
+    if (i < taps - 1) {
+      const int rel = j0 - (taps - 1) + i;
+      if (rel >= 0) v.load(x + (int64_t)(t0 + rel) * ldx + c);
+      else if (carried) v.load(st + (int64_t)(taps - 1 + rel) * C + c);
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) win[i][e] = v.get(e);
+  }
+  const int j1 = min(j0 + CONV_TOK_TILE, qlen);
+  for (int j = j0; j < j1; ++j) {
+    Vec16<T> v, o;
+    v.load(x + (int64_t)(t0 + j) * ldx + c);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      const float cur = v.get(e);
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < CONV_VEC_TAPS - 1; ++i)
+        if (i < taps - 1) acc = fmaf(wt[i][e], win[i][e], acc);
+#pragma unroll
+      for (int i = 0; i < CONV_VEC_TAPS; ++i)
+        if (i == taps - 1) acc = fmaf(wt[i][e], cur, acc);
+      o.set(e, apply_silu ? conv_silu<T>(acc) : acc);
+#pragma unroll
+      for (int i = 0; i < CONV_VEC_TAPS - 1; ++i) {
+        if (i < taps - 2) win[i][e] = win[i + 1][e];
+        else if (i == taps - 2) win[i][e] = cur;
+      }
+    }
+    o.store(out + (int64_t)(t0 + j) * ldo + c);
   }
 }
 
@@ -377,25 +444,37 @@ __global__ void __launch_bounds__(256) gated_group_rmsnorm_kernel(const float* _
   }
 }
 
-// one CTA per token row.  x (fp32) += mult * y / rms(y) * (offset + w); h = cast(x)
-template <typename T>
+// one CTA per token row.  x (fp32) += mult * y / rms(y) * (offset + w); h = cast(x).  VEC = 4: 16-byte accesses of the
+// stream, 8-byte ones of 16-bit operands (row width and strides multiples of 4, checked by the launcher).
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) rmsnorm_residual_kernel(float* __restrict__ x, const T* __restrict__ y, int64_t ldy,
                                                                const T* __restrict__ w, T* __restrict__ h, int W,
                                                                float eps, float mult, float offset) {
+  struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
+  struct alignas(sizeof(float) * VEC) PackF { float v[VEC]; };
   __shared__ float red[64];
   const int64_t t = blockIdx.x;
   const T* yr = y + t * ldy;
   float ss[1] = {0.f};
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float a = to_f32<T>(yr[i]);
-    ss[0] = fmaf(a, a, ss[0]);
+  for (int i = threadIdx.x * VEC; i < W; i += blockDim.x * VEC) {
+    const Pack a = *reinterpret_cast<const Pack*>(yr + i);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) ss[0] = fmaf(to_f32<T>(a.v[e]), to_f32<T>(a.v[e]), ss[0]);
   }
   block_sum<1>(ss, red);
   const float r = 1.f / sqrtf(ss[0] / (float)W + eps);
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float nx = x[t * W + i] + mult * (to_f32<T>(yr[i]) * r * (offset + to_f32<T>(w[i])));
-    x[t * W + i] = nx;
-    if (h != nullptr) h[t * W + i] = from_f32<T>(nx);
+  for (int i = threadIdx.x * VEC; i < W; i += blockDim.x * VEC) {
+    const Pack a = *reinterpret_cast<const Pack*>(yr + i);
+    const Pack ww = *reinterpret_cast<const Pack*>(w + i);
+    PackF xv = *reinterpret_cast<const PackF*>(x + t * W + i);
+    Pack hv;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      xv.v[e] += mult * (to_f32<T>(a.v[e]) * r * (offset + to_f32<T>(ww.v[e])));
+      hv.v[e] = from_f32<T>(xv.v[e]);
+    }
+    *reinterpret_cast<PackF*>(x + t * W + i) = xv;
+    if (h != nullptr) *reinterpret_cast<Pack*>(h + t * W + i) = hv;
   }
 }
 
@@ -840,8 +919,17 @@ int cb_short_conv_silu(const void* x, int64_t ldx, const void* w, void* state, v
   if (nseq == 0 || max_q == 0) return 0;
   dim3 grid((C + 127) / 128, (max_q + CONV_TOK_TILE - 1) / CONV_TOK_TILE, nseq);
   CB_DISPATCH_FLOAT(dtype, T, {
-    short_conv_silu_kernel<T><<<grid, 128, 0, st>>>((const T*)x, ldx, (const T*)w, (const T*)state, (T*)out, ldo, cu_q,
-                                                    ctx_len, slots, C, taps, apply_silu);
+    constexpr int V = Vec16<T>::N;
+    const bool vec = taps <= CONV_VEC_TAPS && C % V == 0 && ldx % V == 0 && ldo % V == 0 && ((uintptr_t)x % 16) == 0 &&
+                     ((uintptr_t)out % 16) == 0 && ((uintptr_t)state % 16) == 0;
+    if (vec) {
+      dim3 vgrid((C / V + 127) / 128, grid.y, grid.z);
+      short_conv_silu_vec_kernel<T><<<vgrid, 128, 0, st>>>((const T*)x, ldx, (const T*)w, (const T*)state, (T*)out, ldo,
+                                                          cu_q, ctx_len, slots, C, taps, apply_silu);
+    } else {
+      short_conv_silu_kernel<T><<<grid, 128, 0, st>>>((const T*)x, ldx, (const T*)w, (const T*)state, (T*)out, ldo, cu_q,
+                                                      ctx_len, slots, C, taps, apply_silu);
+    }
     if (update_state && taps > 1)
       short_conv_state_kernel<T><<<dim3((C + 127) / 128, nseq), 128, 0, st>>>((const T*)x, ldx, (T*)state, cu_q, ctx_len,
                                                                              slots, C, taps);
@@ -889,8 +977,14 @@ int cb_rmsnorm_residual(float* x, const void* y, int64_t ldy, const void* w, voi
                         float mult, float offset, int dtype, cudaStream_t st) {
   if (tokens == 0) return 0;
   CB_DISPATCH_FLOAT(dtype, T, {
-    rmsnorm_residual_kernel<T><<<(unsigned)tokens, 256, 0, st>>>(x, (const T*)y, ldy, (const T*)w, (T*)h, W, eps, mult,
-                                                                offset);
+    const bool vec = W % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)y % (4 * sizeof(T))) == 0 &&
+                     ((uintptr_t)w % (4 * sizeof(T))) == 0 && ((uintptr_t)h % (4 * sizeof(T))) == 0 && ((uintptr_t)x % 16) == 0;
+    if (vec)
+      rmsnorm_residual_kernel<T, 4><<<(unsigned)tokens, 256, 0, st>>>(x, (const T*)y, ldy, (const T*)w, (T*)h, W, eps,
+                                                                     mult, offset);
+    else
+      rmsnorm_residual_kernel<T, 1><<<(unsigned)tokens, 256, 0, st>>>(x, (const T*)y, ldy, (const T*)w, (T*)h, W, eps,
+                                                                     mult, offset);
   });
   return CB_LAUNCH_CHECK();
 }

@@ -41,6 +41,9 @@ _workspaces = {}
 
 def _workspace(name: str, numel: int, device) -> torch.Tensor:
     """Grow-only fp32 scratch per (purpose, device): consecutive layers run on one stream, so they can share it."""
+    if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
+        # a captured step keeps its own scratch in the graph's pool: the shared one may be regrown (freed) later
+        return torch.empty(max(int(numel), 1), dtype=torch.float32, device=device)
     key = (name, str(device))
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < numel:
@@ -77,6 +80,28 @@ class RaggedMeta:
     @property
     def max_q(self) -> int:
         return max(self.q_lens) if self.q_lens else 0
+
+    @staticmethod
+    def layout(flat: torch.Tensor, nseq: int, tokens: int):
+        """Views of one flat int32 buffer [cu_q | ctx_len | slots | token_seq | token_pos]."""
+        a, b, c, d = nseq + 1, 2 * nseq + 1, 3 * nseq + 1, 3 * nseq + 1 + tokens
+        return flat[:a], flat[a:b], flat[b:c], flat[c:d], flat[d:d + tokens]
+
+    @staticmethod
+    def flat_list(q_lens: Sequence[int], ctx_lens: Sequence[int], slots: Sequence[int]) -> List[int]:
+        cu, seq, pos = [0], [], []
+        for i, (n, c) in enumerate(zip(q_lens, ctx_lens)):
+            cu.append(cu[-1] + int(n))
+            seq += [i] * int(n)
+            pos += range(int(c), int(c) + int(n))
+        return cu + [int(c) for c in ctx_lens] + [int(x) for x in slots] + seq + pos
+
+    @staticmethod
+    def decode_static(flat: torch.Tensor, nseq: int, max_ctx: int) -> "RaggedMeta":
+        """One token per sequence over a fixed device buffer (CUDA-graph replay refills `flat`): the host-side mirror
+        holds the worst case (`max_ctx` cached tokens) so that launch shapes do not depend on the step."""
+        cu, ctx, slots, seq, pos = RaggedMeta.layout(flat, nseq, nseq)
+        return RaggedMeta(cu, ctx, slots, seq, pos, [1] * nseq, [max_ctx] * nseq, list(range(nseq)))
 
     @staticmethod
     def build(q_lens: Sequence[int], ctx_lens: Sequence[int], slots: Sequence[int], device) -> "RaggedMeta":

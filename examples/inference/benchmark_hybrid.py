@@ -70,10 +70,11 @@ def build(cfg: ModelConfig):
     return model.eval()
 
 
-def serve(cfg: ModelConfig, batch: int, in_len: int, out_len: int) -> dict:
+def serve(cfg: ModelConfig, batch: int, in_len: int, out_len: int, cuda_graph: bool = False) -> dict:
     model = build(cfg)
     icfg = InferenceConfig(max_batch_size=batch, max_input_len=in_len, max_output_len=out_len, dtype="bf16",
-                           block_size=64, ignore_eos=True, max_num_batched_tokens=batch * in_len)
+                           block_size=64, ignore_eos=True, max_num_batched_tokens=batch * in_len,
+                           use_cuda_graph=cuda_graph)
     eng = LLMEngine(model, None, icfg)
     gen = GenerationConfig(max_new_tokens=out_len)
     eng.generation_config, eng.generation_config_dict = gen, gen.to_dict()
@@ -103,7 +104,7 @@ def serve(cfg: ModelConfig, batch: int, in_len: int, out_len: int) -> dict:
     tp, td, steps = run()
     n_params = sum(p.numel() for p in model.parameters())
     out = {"family": cfg.model_type, "width": cfg.hidden_size, "layers": cfg.num_hidden_layers, "params": n_params,
-           "batch": batch, "in_len": in_len, "out_len": out_len, "prefill_ms": tp,
+           "batch": batch, "in_len": in_len, "out_len": out_len, "cuda_graph": cuda_graph, "prefill_ms": tp,
            "prefill_tokens_per_s": batch * in_len / (tp / 1e3), "decode_ms_per_step": td / max(steps, 1),
            "decode_tokens_per_s": batch * steps / (td / 1e3), "our_kernel_launches": loader.launch_counter.count}
     del eng, model
@@ -205,6 +206,7 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--in_len", type=int, default=2048)
     ap.add_argument("--out_len", type=int, default=32)
+    ap.add_argument("--cuda_graph", action="store_true", help="also run both families with CUDA-graph decode steps")
     ap.add_argument("--no-kernels", action="store_true")
     ap.add_argument("--no-serve", action="store_true")
     args = ap.parse_args(argv)
@@ -212,8 +214,9 @@ def main(argv=None):
     for size in args.sizes.split(","):
         width, layers = (int(z) for z in size.split("x"))
         if not args.no_serve:
-            for cfg in (hybrid_config(width, layers), llama_config(width, layers)):
-                print(json.dumps(serve(cfg, args.batch, args.in_len, args.out_len)), flush=True)
+            for graph in ([False, True] if args.cuda_graph else [False]):
+                for cfg in (hybrid_config(width, layers), llama_config(width, layers)):
+                    print(json.dumps(serve(cfg, args.batch, args.in_len, args.out_len, graph)), flush=True)
         if not args.no_kernels:
             for row in kernels(width, args.batch, args.in_len):
                 print(json.dumps(row), flush=True)

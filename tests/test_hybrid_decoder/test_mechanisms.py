@@ -51,10 +51,11 @@ def test_bucket_starts_match_the_formula(device, B, D):
 @pytest.mark.parametrize("device", DEVICES)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("taps,cuts", [(4, [1, 1, 2, 9, 3]), (3, [40]), (2, [2, 2, 1]), (1, [5, 1]), (5, [1, 1, 1, 1, 1, 1])])
-def test_short_conv_carries_its_window(device, dtype, taps, cuts):
+@pytest.mark.parametrize("C", [70, 72])              # 72: the 16-byte vector kernel; 70: the scalar one
+def test_short_conv_carries_its_window(device, dtype, taps, cuts, C):
     dev = _dev(device)
     g = torch.Generator().manual_seed(taps)
-    C, L, slots = 70, 44, 3
+    L, slots = 44, 3
     x = torch.randn(L, C, generator=g).to(dtype)
     w = (torch.randn(C, taps, generator=g) * 0.5).to(dtype)
     want = O.silu(O.short_conv(x.double(), w.double()))
@@ -150,10 +151,11 @@ def test_scans_keep_sequences_of_a_batch_apart(device):
 
 @pytest.mark.parametrize("device", DEVICES)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_norm_kernels(device, dtype):
+@pytest.mark.parametrize("W", [72, 75])
+def test_norm_kernels(device, dtype, W):
     dev = _dev(device)
     g = torch.Generator().manual_seed(3)
-    T, H, dv, W = 7, 3, 40, 72
+    T, H, dv = 7, 3, 40
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     o, gate = torch.randn(T, H * dv, generator=g) * 3, torch.randn(T, H * dv, generator=g).to(dtype)
     for group, w in ((dv, torch.randn(dv, generator=g).to(dtype)), (H * dv, torch.randn(H * dv, generator=g).to(dtype))):
