@@ -44,7 +44,7 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--workload", default="train", choices=["train", "hybrid-serve"],
-                   help="train: the headline training step (default, the contract above).  hybrid-serve: prefill / decode "
+                   help="train: the headline training step (default, described above).  hybrid-serve: prefill / decode "
                         "throughput of the hybrid decoder beside Llama at equal size and its kernels against their "
                         "rooflines (examples/inference/benchmark_hybrid.py; extra flags are passed on)")
     p.add_argument("--model", default=os.environ.get("CB200_BENCH_MODEL", "llama3-8b"))

@@ -12,8 +12,9 @@
 // depend on how the prompt was cut or on what else is in the batch.
 //
 //   cb_short_conv_silu      y = silu(causal depthwise conv(x)) over time, window of taps-1 inputs carried per slot
-//   cb_state_scan           (prepare + scan) S <- decay * S + k (x) v   (scalar decay per head), or the gated delta rule
-//                           S <- g * S; u = beta (v - S^T k); S <- S + k (x) u  (decay per key channel); o = S^T q
+//   cb_state_scan           (prepare + scan) per head a matrix M [dim, vdim]: either M <- a_h M + outer(k, v) with one
+//                           decay per head, or the gated delta rule M <- diag(r) M; e = w (v - M^T k); M <- M + outer(k, e)
+//                           with a decay per key channel; the read-out y = M^T q follows the write
 //   cb_gated_group_rmsnorm  out = o / rms_group(o) * w * sigmoid(gate)
 //   cb_rmsnorm_residual     x(fp32) += mult * y / rms(y) * (offset + w);  h = cast(x)
 //   cb_rmsnorm_f32in        out = cast(x / rms(x) * (offset + w)) for an fp32 residual stream
@@ -174,7 +175,7 @@ __global__ void __launch_bounds__(128) short_conv_state_kernel(const T* __restri
 
 // ------------------------------------------------------------------------------------------------ recurrent state scan
 enum ScanMode : int { SCAN_DECAY = 0, SCAN_DELTA = 1 };
-constexpr int SCAN_TOK_TILE = 16;
+constexpr int SCAN_TOK_TILE = 8;
 
 struct ScanParams {
   const void *q, *k, *v;        // [T, ld*]: q/k hold qk_heads x dim, v holds heads x vdim
@@ -266,7 +267,7 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(ScanParams p, ScanWor
 }
 
 template <int DK, int MODE>
-__global__ void __launch_bounds__(128, 3) state_scan_kernel(ScanParams p, ScanWork w) {
+__global__ void __launch_bounds__(128, 4) state_scan_kernel(ScanParams p, ScanWork w) {
   constexpr int RP = DK / SCAN_PARTS;  // rows per lane
   constexpr int RPP = RP + 4;          // a lane's rows start 4 floats further: the four 16-byte reads of a warp hit
   constexpr int DKP = SCAN_PARTS * RPP;  // different banks

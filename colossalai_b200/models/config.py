@@ -131,7 +131,7 @@ class ModelConfig:
     layer_specs: Optional[List[LayerSpec]] = None
     norm_placement: str = "pre"       # "pre": sublayer(norm(x)); "sublayer_out": x + residual_mult * norm(sublayer(x))
     residual_mult: float = 1.0
-    norm_weight_offset: float = 0.0   # weights stored around zero: the norm multiplies by (offset + w)
+    norm_weight_offset: float = 0.0   # zero-centred norm weights: the norm multiplies by (offset + w)
     fp32_residual: bool = False       # the residual stream stays in fp32 whatever the compute dtype
     pad_token_id: Optional[int] = None
     bos_token_id: int = 1

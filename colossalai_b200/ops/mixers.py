@@ -120,8 +120,8 @@ class RaggedMeta:
 
 def log_bucket_starts(num_buckets: int, max_distance: float) -> List[int]:
     """Smallest distance that falls into every bucket of a table whose first half is exact and whose second half is
-    logarithmic up to `max_distance`: bucket(n) = n for n < B/2, else
-    min(B - 1, B/2 + floor(ln(n / (B/2)) / ln(max_distance / (B/2)) * (B - B/2)))."""
+    logarithmic up to `max_distance`.  With h = B // 2 rows for the exact part, a distance below h is its own row and
+    a distance n >= h lands in row h + floor((B - h) * log(n / h) / log(max_distance / h)), clipped to the last row."""
     B, half = num_buckets, num_buckets // 2
 
     def bucket(n: int) -> int:
@@ -205,8 +205,8 @@ def _scan_native(mode, q, k, v, araw, braw, head_decay, a_log, dt_bias, state, m
 
 def state_scan_decay(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, head_decay: torch.Tensor, state: torch.Tensor,
                      meta: RaggedMeta, heads: int, dim: int, vdim: int, act_silu: bool = True) -> torch.Tensor:
-    """Decayed outer-product memory per head: S <- decay_h S + k v^T, o = S^T q (q, k, v through silu first when
-    `act_silu`).  q, k [T, heads x dim], v [T, heads x vdim]; state [slots, heads, dim, vdim] fp32.  Returns fp32 o."""
+    """Decayed outer-product memory per head: every token scales the head's matrix M [dim, vdim] by the head's decay,
+    adds outer(k, v) and reads y = M^T q (q, k, v through silu first when `act_silu`).  q, k [T, heads x dim], v [T, heads x vdim]; state [slots, heads, dim, vdim] fp32.  Returns fp32 o."""
     if dim > 128:
         raise NotImplementedError("state_scan: key width above 128 is not supported")
     if use_native(q):
@@ -237,8 +237,9 @@ def state_scan_delta(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_pr
                      qk_heads: int, dim: int, vdim: int, unit_eps: float = 1e-6,
                      q_scale: Optional[float] = None) -> torch.Tensor:
     """Gated delta rule with one decay per head and key channel.  Per token and head: q, k -> unit vectors (q also times
-    `q_scale`), g = exp(-exp(a_log_h) softplus(decay_pre + dt_bias)), beta = sigmoid(beta_pre);
-    S <- g S (rows); u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  q, k [T, qk_heads x dim] (head h reads
+    `q_scale`), row decays r = exp(-exp(a_log_h) * softplus(decay_pre + dt_bias)), write strength w = sigmoid(beta_pre);
+    the head's matrix M [dim, vdim] is first decayed row by row (M <- diag(r) M), then corrected towards v along k
+    (e = w * (v - M^T k); M <- M + outer(k, e)) and read after the write (y = M^T q).  q, k [T, qk_heads x dim] (head h reads
     h // (heads / qk_heads)), v [T, heads x vdim], decay_pre [T, heads x dim], beta_pre [T, heads]; fp32 state."""
     if dim > 128:
         raise NotImplementedError("state_scan: key width above 128 is not supported")

@@ -41,7 +41,8 @@ def short_conv(z, w):
 
 
 def lightning(q, k, v, decay):
-    """q, k [L, H, d], v [L, H, dv]; S_t = decay_h S_(t-1) + k_t v_t^T; o_t = S_t^T q_t."""
+    """q, k [L, H, d], v [L, H, dv].  Per head a matrix M [d, dv], zero at the start: each token first shrinks M by
+    the head's decay, then adds outer(k, v), then reads M^T q."""
     L, H, d = q.shape
     S = torch.zeros(H, d, v.shape[-1], dtype=F64)
     out = []
@@ -53,8 +54,9 @@ def lightning(q, k, v, decay):
 
 
 def delta_rule(q, k, v, g, beta):
-    """q, k [L, H, d] (already unit / scaled), v [L, H, dv], g [L, H, d], beta [L, H].
-    S <- g S (rows); u = beta (v - S^T k); S <- S + k u^T; o = S^T q."""
+    """q, k [L, H, d] (already unit / scaled), v [L, H, dv], g [L, H, d] row decays, beta [L, H] write strengths.
+    Per head a matrix M [d, dv], zero at the start; each token: rows of M times g; error = beta * (v - M^T k);
+    M gains outer(k, error); the read-out M^T q comes after the write."""
     L, H, d = q.shape
     S = torch.zeros(H, d, v.shape[-1], dtype=F64)
     out = []
@@ -70,8 +72,8 @@ def delta_rule(q, k, v, g, beta):
 
 
 def sink_attention(q, k, v, scale, rel, D):
-    """q [L, H, d], k [L, G, d], v [L, G, dv]; causal; score = scale q.k + rel[bucket(i - j), h];
-    p_j = exp(s_j) / (1 + sum exp(s_j))."""
+    """q [L, H, d], k [L, G, d], v [L, G, dv].  Token i scores every j <= i with scale * <q_i, k_j> plus the table entry
+    of (bucket of i - j, head); the softmax has an extra term exp(0) in its denominator that carries no value."""
     L, H, _ = q.shape
     G = k.shape[1]
     out = torch.zeros(L, H, v.shape[-1], dtype=F64)
