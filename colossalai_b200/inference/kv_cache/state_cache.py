@@ -52,7 +52,7 @@ class StateCacheManager:
         self.dtype = config.dtype
         self._free: List[int] = list(range(self.num_slots))
         self.states: List[Optional[Dict[str, torch.Tensor]]] = []
-        for i in range(model_config.num_hidden_layers):
+        for i in range(model_config.num_hidden_layers):      # models without recurrent layers only use the slot ids
             shapes = layer_state_shapes(model_config, i, self.num_slots)
             self.states.append(None if shapes is None else {
                 n: torch.zeros(s, dtype=torch.float32 if n == "S" else self.dtype, device=self.device)

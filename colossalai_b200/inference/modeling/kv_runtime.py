@@ -40,6 +40,7 @@ class PagedKVRuntime:
         """Prepare per-step metadata; returns the int64 position of every input token."""
         self.block_tables = block_tables.to(device=device, dtype=torch.int32).contiguous()
         self.seq_lens = seq_lens.to(device=device, dtype=torch.int32).contiguous()
+        self.ragged = None
         self.is_prompt = is_prompt
         self.q_per_seq = q_per_seq
         lens = seq_lens.tolist()
@@ -124,6 +125,14 @@ class PagedKVRuntime:
 
     def attend(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta, scale: float,
                alibi_slopes: Optional[torch.Tensor] = None, sliding_window: Optional[int] = None) -> torch.Tensor:
+        if self.ragged is not None:
+            # a ragged step (portions of prompts beside decoded tokens): rotary / plain attention families take the same
+            # paged kernels as the hybrid decoders, without bias table and sink
+            if alibi_slopes is not None or sliding_window is not None:
+                raise NotImplementedError("ragged steps (chunked prefill) do not cover ALiBi or sliding-window attention")
+            T, hq = q.shape[0], q.shape[1]
+            o = self.attend_ragged(layer_idx, q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1), scale)
+            return o.view(T, hq, -1)
         kc, vc = self.k_caches[layer_idx], self.v_caches[layer_idx]
         iops.kv_cache_write(k, v, kc, vc, self.block_tables, self.token_seq, self.token_pos)
         if sliding_window is not None and self.max_len_host > sliding_window:

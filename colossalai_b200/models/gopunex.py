@@ -1,7 +1,7 @@
 """Gopunex: a hybrid decoder whose layers mix tokens by softmax attention with a distance-bucket bias and a sink, by
 lightning (decayed linear) attention, or by a channel-wise gated delta rule, in any order; every sublayer's OUTPUT is
-RMS-normalised with zero-centred weights (the norm multiplies by 1 + w), scaled and added to an fp32 residual stream; dense feed-forwards use the
-squared ReLU.
+RMS-normalised with zero-centred weights (the norm multiplies by 1 + w), scaled and added to an fp32 residual stream;
+dense feed-forwards use the squared ReLU.
 
 The model is the generic backbone (`transformer.py`) configured by `ModelConfig.layer_specs`; this module only reads the
 family's `config.json` / tensor names.  A checkpoint is `config.json` + `model.safetensors` with

@@ -238,3 +238,23 @@ def test_replay_command_writes_the_logits_asked_for(tmp_path, tier):
     _check(g1, wb[[5]], 2e-4)
     _check(g2, wa[[19]], 2e-4)
     assert sorted(os.listdir(out)) == ["0.f32", "1.f32", "2.f32"]
+
+
+@pytest.mark.parametrize("tier", TIERS)
+def test_chunked_prefill_serves_a_rotary_model_like_whole_prompts(tier):
+    """A Llama through the ragged scheduler (prompts cut by a small token budget, portions beside decoded tokens, fewer
+    slots than requests) generates what the whole-prompt scheduler generates."""
+    _tier(tier)
+    from colossalai_b200.models import build_model, get_config
+
+    torch.manual_seed(0)
+    cfg = get_config("llama-tiny")
+    model = build_model(cfg).eval()
+    prompts = [_tokens(n, cfg.vocab_size, 50 + n) for n in (37, 5, 18)]
+    out = {}
+    for chunked in (False, True):
+        icfg = InferenceConfig(dtype=torch.float32, max_batch_size=2 if chunked else 3, max_input_len=64, max_output_len=6,
+                               block_size=8, ignore_eos=True, enable_chunked_prefill=chunked, max_num_batched_tokens=11)
+        eng = LLMEngine(model, None, icfg)
+        _, out[chunked] = eng.generate(prompts_token_ids=[list(p) for p in prompts], return_token_ids=True)
+    assert out[True] == out[False]
