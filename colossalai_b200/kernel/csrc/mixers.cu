@@ -391,7 +391,12 @@ template <int DK, int MODE> int launch_scan_dk(const ScanParams& p, const ScanWo
   constexpr int NROW = MODE == SCAN_DELTA ? 3 : 2;
   const size_t smem = (size_t)2 * SCAN_TOK_TILE * (NROW * DKP + SCAN_COLS + 4) * sizeof(float);
   auto kern = state_scan_kernel<DK, MODE>;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+    configured = true;
+  }
   dim3 grid(p.heads * (w.VP / SCAN_COLS), nseq);
   kern<<<grid, SCAN_COLS * SCAN_PARTS, smem, st>>>(p, w);
   return CB_LAUNCH_CHECK();
@@ -638,20 +643,32 @@ CB_DEVICE void cp_async16(void* smem_dst, const void* gmem_src, uint32_t src_byt
 // Key range split (decode steps, few CTAs): with `chunk` > 0 grid.x also enumerates key chunks; a CTA then writes its
 // unnormalised partial (fp32 accumulator, running maximum, denominator without the sink) and `attention_merge_kernel`
 // joins the chunks of every (token, head) in ascending order.
-template <typename T, int D, int NW>
-__global__ void __launch_bounds__(NW * 32) paged_bias_attention_mma_kernel(
+//
+// A CTA is 4 warps x 32 rows (MT = 2 m16 tiles per warp) when a portion fills 128 rows, 4 x 16 (MT = 1) otherwise.  Two
+// m-tiles per warp halve the shared-memory reads per MMA (a K / V fragment feeds both) and double the independent
+// accumulator chains.  The query tile sits in shared memory (A fragments by ldmatrix.x4, K fragments by ldmatrix.x4
+// for two k-steps at once, V fragments by ldmatrix.x2.trans).
+CB_DEVICE void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+template <typename T, int D, int MT>
+__global__ void __launch_bounds__(128, MT == 2 ? 2 : 3) paged_bias_attention_mma_kernel(
     const T* __restrict__ q, int64_t ldq, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const float* __restrict__ bias_table, const uint8_t* __restrict__ lut, int lut_n, int nbuckets, T* __restrict__ out,
     int heads, int kv_heads, int dim, int vdim, int block_size, int max_blocks, float scale, int sink, int chunk,
     int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
-  constexpr int BM = NW * 16;
+  constexpr int BM = 64 * MT;
   constexpr int LDS = D + 8;                    // padded row: 16-byte aligned, conflict-free fragment reads
   constexpr int TILE = MMA_BN * LDS;
+  constexpr int NR = 2 * MT;                    // rows a thread owns: (m-tile, upper / lower half)
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* KV = reinterpret_cast<T*>(smem_raw);       // [2 stages][K tile | V tile]
-  float* tab = reinterpret_cast<float*>(KV + 4 * TILE);             // [nbuckets][R] of this kv head's group
+  T* Qs = KV + 4 * TILE;                        // [BM][LDS]
+  float* tab = reinterpret_cast<float*>(Qs + BM * LDS);              // [nbuckets][R] of this kv head's group
   const int s = blockIdx.z, g = blockIdx.y;
   const int R = heads / kv_heads;
   const int t0 = cu_q[s], qlen = cu_q[s + 1] - t0;
@@ -664,47 +681,14 @@ __global__ void __launch_bounds__(NW * 32) paged_bias_attention_mma_kernel(
   const int pos_max = chunk > 0 ? min(ctx + last_row / R, key_lo + chunk - 1) : ctx + last_row / R;
   if (key_lo > pos_max) return;                 // this chunk lies beyond every row of the tile
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
-  for (int i = tid; i < nbuckets * R; i += NW * 32) tab[i] = bias_table[(i / R) * heads + g * R + (i % R)] * LOG2E;
+  for (int i = tid; i < nbuckets * R; i += 128) tab[i] = bias_table[(i / R) * heads + g * R + (i % R)] * LOG2E;
   const int* bt = block_tables + (int64_t)s * max_blocks;
-
-  int rr[2], pos[2], hr[2];
-  bool valid[2];
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    rr[e] = row0 + warp * 16 + gid + 8 * e;
-    valid[e] = rr[e] < nrows;
-    hr[e] = valid[e] ? rr[e] % R : 0;
-    pos[e] = valid[e] ? ctx + rr[e] / R : -1;
-  }
-  uint32_t qf[D / 16][4];
-#pragma unroll
-  for (int ks = 0; ks < D / 16; ++ks)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int r = e & 1, col = ks * 16 + tig * 2 + ((e >> 1) ? 8 : 0);
-      uint32_t val = 0;
-      if (valid[r] && col < dim)
-        val = *reinterpret_cast<const uint32_t*>(q + (int64_t)(t0 + rr[r] / R) * ldq + (g * R + hr[r]) * dim + col);
-      qf[ks][e] = val;
-    }
-  float o[D / 8][4];
-#pragma unroll
-  for (int nv = 0; nv < D / 8; ++nv)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) o[nv][e] = 0.f;
-  float m[2], l[2];
-  m[0] = m[1] = (sink && chunk == 0) ? 0.f : -INFINITY;     // log2 domain; with chunks the sink joins in the merge
-  l[0] = l[1] = 0.f;                            // per-thread partial; the sink's share is added once at the end
-  const float sc2 = scale * LOG2E;
-  // first / last position any row of this warp sees: tiles beyond are skipped, tiles before need no causal test
-  const int wlo = ctx + min(nrows - 1, row0 + warp * 16) / R;
-  const int whi = ctx + min(nrows - 1, row0 + warp * 16 + 15) / R;
 
   auto load_tile = [&](int stage, int j0) {
     constexpr int CH = D / 8;
     T* Ks = KV + stage * 2 * TILE;
     T* Vs = Ks + TILE;
-    for (int idx = tid; idx < MMA_BN * CH; idx += NW * 32) {
+    for (int idx = tid; idx < MMA_BN * CH; idx += 128) {
       const int r = idx / CH, c8 = (idx % CH) * 8;
       const int j = j0 + r;
       const bool in = j <= pos_max;
@@ -715,8 +699,48 @@ __global__ void __launch_bounds__(NW * 32) paged_bias_attention_mma_kernel(
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-
+  {                                             // the query tile rides in the first copy group
+    constexpr int CH = D / 8;
+    for (int idx = tid; idx < BM * CH; idx += 128) {
+      const int r = idx / CH, c8 = (idx % CH) * 8;
+      const int row = row0 + r;
+      const bool in = row < nrows && c8 < dim;
+      cp_async16(Qs + r * LDS + c8, q + (in ? (int64_t)(t0 + row / R) * ldq + (g * R + row % R) * dim + c8 : 0),
+                 in ? 16u : 0u);
+    }
+  }
   load_tile(0, key_lo);
+
+  int rr[NR], pos[NR], hr[NR];
+  bool valid[NR];
+#pragma unroll
+  for (int e = 0; e < NR; ++e) {
+    rr[e] = row0 + warp * (16 * MT) + (e >> 1) * 16 + gid + 8 * (e & 1);
+    valid[e] = rr[e] < nrows;
+    hr[e] = valid[e] ? rr[e] % R : 0;
+    pos[e] = valid[e] ? ctx + rr[e] / R : -1;
+  }
+  float o[MT][D / 8][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nv = 0; nv < D / 8; ++nv)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[mt][nv][e] = 0.f;
+  float m[NR], l[NR];
+#pragma unroll
+  for (int e = 0; e < NR; ++e) {
+    m[e] = (sink && chunk == 0) ? 0.f : -INFINITY;          // log2 domain; with chunks the sink joins in the merge
+    l[e] = 0.f;                                 // per-thread partial; the sink's share is added once at the end
+  }
+  const float sc2 = scale * LOG2E;
+  // first / last position any row of this warp sees: tiles beyond are skipped, tiles before need no causal test
+  const int wrow0 = row0 + warp * (16 * MT);
+  const bool wlive = wrow0 < nrows;
+  const int wlo = ctx + min(nrows - 1, wrow0) / R;
+  const int whi = wlive ? ctx + min(nrows - 1, wrow0 + 16 * MT - 1) / R : -1;
+  const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + (warp * 16 * MT + (lane & 15)) * LDS + (lane >> 4) * 8);
+
   int stage = 0;
   for (int j0 = key_lo; j0 <= pos_max; j0 += MMA_BN, stage ^= 1) {
     if (j0 + MMA_BN <= pos_max) {               // the other stage was released by the barrier that ended the last pass
@@ -729,56 +753,76 @@ __global__ void __launch_bounds__(NW * 32) paged_bias_attention_mma_kernel(
     if (j0 <= whi) {                            // warp-uniform: otherwise the whole tile is masked for this warp
       const T* Ks = KV + stage * 2 * TILE;
       const T* Vs = Ks + TILE;
-      float sacc[MMA_BN / 8][4];
+      float sacc[MT][MMA_BN / 8][4];
 #pragma unroll
-      for (int nt = 0; nt < MMA_BN / 8; ++nt) {
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) sacc[nt][e] = 0.f;
+        for (int nt = 0; nt < MMA_BN / 8; ++nt)
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const T* kp = Ks + (nt * 8 + gid) * LDS + ks * 16 + tig * 2;
-          mma_16816<T>(sacc[nt], qf[ks], *reinterpret_cast<const uint32_t*>(kp),
-                       *reinterpret_cast<const uint32_t*>(kp + 8));
+          for (int e = 0; e < 4; ++e) sacc[mt][nt][e] = 0.f;
+      const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(Ks + (lane & 7) * LDS + (lane >> 3) * 8);
+#pragma unroll
+      for (int kp = 0; kp < D / 32; ++kp) {     // two k-steps of 16 per pass
+        uint32_t qa[MT][2][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          ldsm_x4(qa[mt][0], q_addr + (mt * 16 * LDS + kp * 32) * (uint32_t)sizeof(T));
+          ldsm_x4(qa[mt][1], q_addr + (mt * 16 * LDS + kp * 32 + 16) * (uint32_t)sizeof(T));
+        }
+#pragma unroll
+        for (int nt = 0; nt < MMA_BN / 8; ++nt) {
+          uint32_t kb[4];
+          ldsm_x4(kb, k_addr + (nt * 8 * LDS + kp * 32) * (uint32_t)sizeof(T));
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma_16816<T>(sacc[mt][nt], qa[mt][0], kb[0], kb[1]);
+            mma_16816<T>(sacc[mt][nt], qa[mt][1], kb[2], kb[3]);
+          }
         }
       }
       const bool unmasked = j0 + MMA_BN - 1 <= wlo;
       const bool far = nbuckets == 0 || wlo - (j0 + MMA_BN - 1) >= lut_n;     // every distance in the last bucket
-      float fb[2] = {0.f, 0.f};
-      if (nbuckets > 0) {
-        fb[0] = tab[(nbuckets - 1) * R + hr[0]];
-        fb[1] = tab[(nbuckets - 1) * R + hr[1]];
-      }
-      float mx[2] = {m[0], m[1]};
+      float fb[NR];
+#pragma unroll
+      for (int e = 0; e < NR; ++e) fb[e] = nbuckets > 0 ? tab[(nbuckets - 1) * R + hr[e]] : 0.f;
+      float mx[NR];
+#pragma unroll
+      for (int e = 0; e < NR; ++e) mx[e] = m[e];
       if (unmasked && far) {
 #pragma unroll
-        for (int nt = 0; nt < MMA_BN / 8; ++nt)
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float sv = fmaf(sacc[nt][e], sc2, fb[e >> 1]);
-            sacc[nt][e] = sv;
-            mx[e >> 1] = fmaxf(mx[e >> 1], sv);
-          }
+          for (int nt = 0; nt < MMA_BN / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int r = mt * 2 + (e >> 1);
+              const float sv = fmaf(sacc[mt][nt][e], sc2, fb[r]);
+              sacc[mt][nt][e] = sv;
+              mx[r] = fmaxf(mx[r], sv);
+            }
       } else {
 #pragma unroll
-        for (int nt = 0; nt < MMA_BN / 8; ++nt)
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int r = e >> 1, j = j0 + nt * 8 + tig * 2 + (e & 1);
-            float sv = -INFINITY;
-            if (j <= pos[r]) {
-              sv = sacc[nt][e] * sc2;
-              if (nbuckets > 0) {
-                const int n = pos[r] - j;
-                sv += n < lut_n ? tab[(int)__ldg(lut + n) * R + hr[r]] : fb[r];
+          for (int nt = 0; nt < MMA_BN / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int r = mt * 2 + (e >> 1), j = j0 + nt * 8 + tig * 2 + (e & 1);
+              float sv = -INFINITY;
+              if (j <= pos[r]) {
+                sv = sacc[mt][nt][e] * sc2;
+                if (nbuckets > 0) {
+                  const int n = pos[r] - j;
+                  sv += n < lut_n ? tab[(int)__ldg(lut + n) * R + hr[r]] : fb[r];
+                }
               }
+              sacc[mt][nt][e] = sv;
+              mx[r] = fmaxf(mx[r], sv);
             }
-            sacc[nt][e] = sv;
-            mx[r] = fmaxf(mx[r], sv);
-          }
       }
-      float alpha[2];
+      float alpha[NR];
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
+      for (int r = 0; r < NR; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         const float mu = mx[r] == -INFINITY ? 0.f : mx[r];
@@ -788,42 +832,52 @@ __global__ void __launch_bounds__(NW * 32) paged_bias_attention_mma_kernel(
         mx[r] = mu;
       }
 #pragma unroll
-      for (int nv = 0; nv < D / 8; ++nv) {
-        o[nv][0] *= alpha[0]; o[nv][1] *= alpha[0];
-        o[nv][2] *= alpha[1]; o[nv][3] *= alpha[1];
-      }
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int nt = 0; nt < MMA_BN / 8; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float pe = ex2f(sacc[nt][e] - mx[e >> 1]);
-          sacc[nt][e] = pe;
-          l[e >> 1] += pe;
+        for (int nv = 0; nv < D / 8; ++nv) {
+          o[mt][nv][0] *= alpha[mt * 2]; o[mt][nv][1] *= alpha[mt * 2];
+          o[mt][nv][2] *= alpha[mt * 2 + 1]; o[mt][nv][3] *= alpha[mt * 2 + 1];
         }
 #pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < MMA_BN / 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int r = mt * 2 + (e >> 1);
+            const float pe = ex2f(sacc[mt][nt][e] - mx[r]);
+            sacc[mt][nt][e] = pe;
+            l[r] += pe;
+          }
+#pragma unroll
       for (int kk = 0; kk < MMA_BN / 16; ++kk) {
-        uint32_t pa[4];
-        pa[0] = pack2<T>(sacc[2 * kk][0], sacc[2 * kk][1]);
-        pa[1] = pack2<T>(sacc[2 * kk][2], sacc[2 * kk][3]);
-        pa[2] = pack2<T>(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
-        pa[3] = pack2<T>(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+        uint32_t pa[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          pa[mt][0] = pack2<T>(sacc[mt][2 * kk][0], sacc[mt][2 * kk][1]);
+          pa[mt][1] = pack2<T>(sacc[mt][2 * kk][2], sacc[mt][2 * kk][3]);
+          pa[mt][2] = pack2<T>(sacc[mt][2 * kk + 1][0], sacc[mt][2 * kk + 1][1]);
+          pa[mt][3] = pack2<T>(sacc[mt][2 * kk + 1][2], sacc[mt][2 * kk + 1][3]);
+        }
         const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(Vs + (kk * 16 + (lane & 15)) * LDS);
 #pragma unroll
         for (int nv = 0; nv < D / 8; ++nv) {
           uint32_t b0, b1;
           asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
                        : "=r"(b0), "=r"(b1) : "r"(vrow + nv * 16));
-          mma_16816<T>(o[nv], pa, b0, b1);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) mma_16816<T>(o[mt][nv], pa[mt], b0, b1);
         }
       }
     }
     __syncthreads();                            // this stage may be refilled in the next pass
   }
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
+  for (int r = 0; r < NR; ++r) {
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
     if (!valid[r]) continue;
+    const int mt = r >> 1, hf = r & 1;
     const int64_t unit = (int64_t)(t0 + rr[r] / R) * heads + g * R + hr[r];
     if (chunk > 0) {
       float* po = part_o + (unit * max_splits + split) * vdim;
@@ -834,7 +888,7 @@ __global__ void __launch_bounds__(NW * 32) paged_bias_attention_mma_kernel(
 #pragma unroll
       for (int nv = 0; nv < D / 8; ++nv) {
         const int c = nv * 8 + tig * 2;
-        if (c < vdim) *reinterpret_cast<float2*>(po + c) = make_float2(o[nv][2 * r], o[nv][2 * r + 1]);
+        if (c < vdim) *reinterpret_cast<float2*>(po + c) = make_float2(o[mt][nv][2 * hf], o[mt][nv][2 * hf + 1]);
       }
       continue;
     }
@@ -844,7 +898,8 @@ __global__ void __launch_bounds__(NW * 32) paged_bias_attention_mma_kernel(
 #pragma unroll
     for (int nv = 0; nv < D / 8; ++nv) {
       const int c = nv * 8 + tig * 2;
-      if (c < vdim) *reinterpret_cast<uint32_t*>(orow + c) = pack2<T>(o[nv][2 * r] * inv, o[nv][2 * r + 1] * inv);
+      if (c < vdim)
+        *reinterpret_cast<uint32_t*>(orow + c) = pack2<T>(o[mt][nv][2 * hf] * inv, o[mt][nv][2 * hf + 1] * inv);
     }
   }
 }
@@ -885,21 +940,28 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const float* __res
   }
 }
 
-template <typename T, int D, int NW>
+template <typename T, int D, int MT>
 int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
                          const int* cu_q, const int* ctx_len, const int* token_pos, const float* bias_table,
                          const uint8_t* lut, int lut_n, int nbuckets, void* out, int64_t tokens, int nseq, int max_q,
                          int heads, int kv_heads, int dim, int vdim, int block_size, int max_blocks, float scale, int sink,
                          int chunk, int max_splits, float* part_o, float* part_ml, cudaStream_t st) {
   const int R = heads / kv_heads;
-  const size_t smem = (size_t)4 * MMA_BN * (D + 8) * sizeof(T) + (size_t)nbuckets * R * sizeof(float);
-  auto kern = paged_bias_attention_mma_kernel<T, D, NW>;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  const int rowtiles = (max_q * R + NW * 16 - 1) / (NW * 16);
+  constexpr int BM = 64 * MT;
+  const size_t smem = (size_t)(4 * MMA_BN + BM) * (D + 8) * sizeof(T) + (size_t)nbuckets * R * sizeof(float);
+  auto kern = paged_bias_attention_mma_kernel<T, D, MT>;
+  static bool configured = false;               // per instantiation: opt in to large shared memory, all of it for CTAs
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+    configured = true;
+  }
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  const int rowtiles = (max_q * R + BM - 1) / BM;
   dim3 grid(rowtiles * (chunk > 0 ? max_splits : 1), kv_heads, nseq);
-  kern<<<grid, NW * 32, smem, st>>>((const T*)q, ldq, (const T*)k_cache, (const T*)v_cache, block_tables, cu_q, ctx_len,
-                                    bias_table, lut, lut_n, nbuckets, (T*)out, heads, kv_heads, dim, vdim, block_size,
-                                    max_blocks, scale, sink, chunk, max_splits, part_o, part_ml);
+  kern<<<grid, 128, smem, st>>>((const T*)q, ldq, (const T*)k_cache, (const T*)v_cache, block_tables, cu_q, ctx_len,
+                                bias_table, lut, lut_n, nbuckets, (T*)out, heads, kv_heads, dim, vdim, block_size,
+                                max_blocks, scale, sink, chunk, max_splits, part_o, part_ml);
   if (chunk > 0) {
     const int64_t units = tokens * heads;
     attention_merge_kernel<T><<<(unsigned)((units + 3) / 4), 128, 0, st>>>(part_o, part_ml, token_pos, (T*)out, tokens,
@@ -1038,17 +1100,17 @@ int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache,
                                 int block_size, int max_blocks, float scale, int sink, int chunk, int max_splits,
                                 float* part_o, float* part_ml, int dtype, cudaStream_t st) {
   if (nseq == 0 || max_q == 0) return 0;
-  if (heads % kv_heads != 0 || dim % 8 != 0 || vdim % 8 != 0 || dim > 128 || vdim > 128 || (ldq & 1) ||
+  if (heads % kv_heads != 0 || dim % 8 != 0 || vdim % 8 != 0 || dim > 128 || vdim > 128 || (ldq & 7) || ((uintptr_t)q & 15) ||
       chunk % MMA_BN != 0)
     return (int)cudaErrorInvalidValue;
   const int dmax = dim > vdim ? dim : vdim;
-  const bool wide = max_q * (heads / kv_heads) > 64;      // 128 query rows per CTA once a portion fills them
+  const bool wide = max_q * (heads / kv_heads) > 64;      // 128 query rows per CTA (32 per warp) once a portion fills them
 #define CB_ATT_MMA(T, D)                                                                                              \
   if (wide)                                                                                                           \
-    return launch_attention_mma<T, D, 8>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table, \
+    return launch_attention_mma<T, D, 2>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table, \
                                          lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,  \
                                          block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, st); \
-  return launch_attention_mma<T, D, 4>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table,  \
+  return launch_attention_mma<T, D, 1>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table,  \
                                        lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,   \
                                        block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, st)
   CB_DISPATCH_HALF(dtype, T, {

@@ -378,7 +378,7 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         assert q.stride(1) == 1 and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
         out = torch.empty(T, heads * vdim, dtype=q.dtype, device=q.device)
         mma_ok = (q.dtype in (torch.bfloat16, torch.float16) and dim % 8 == 0 and vdim % 8 == 0 and dim <= 128
-                  and vdim <= 128 and nb <= 255 and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0)
+                  and vdim <= 128 and nb <= 255 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
         if tensor_cores is None:
             tensor_cores = mma_ok
         if tensor_cores:
