@@ -181,8 +181,11 @@ def kernels(width: int, batch: int, in_len: int) -> list:
         tables = torch.arange(batch * per, dtype=torch.int32, device=dev).view(batch, per)
         qa = x(H * d)
         rel = torch.randn(32, H, device=dev)
-        starts = torch.tensor(M.log_bucket_starts(32, 512.0), dtype=torch.int32, device=dev)
-        ms = _time(lambda: M.paged_bias_attention(qa, kc, vc, tables, meta, d ** -0.5, rel, starts, True), flush)
+        starts_host = M.log_bucket_starts(32, 512.0)
+        starts = torch.tensor(starts_host, dtype=torch.int32, device=dev)
+        lut = M.bucket_lut(starts_host).to(dev)               # built once per layer by the model as well
+        ms = _time(lambda: M.paged_bias_attention(qa, kc, vc, tables, meta, d ** -0.5, rel, starts, True, lut=lut),
+                   flush)
         kv_bytes = 2 * batch * L * G * d * 2
         att_flops = 4.0 * batch * H * d * (q_len * ctx + q_len * (q_len + 1) / 2)
         rec("paged_bias_attention", phase, ms, kv_bytes + 2 * T * H * d * 2, att_flops,
