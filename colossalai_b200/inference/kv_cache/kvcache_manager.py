@@ -200,13 +200,15 @@ class KVCacheManager:
     def _init_device_caches(self):
         if getattr(self.model_config, "layer_specs", None) is not None:
             # hybrid decoders: only attention layers hold pages, and K and V heads may differ in width
-            from .state_cache import layer_cache_shapes
+            # (a looped span of layers holds one cache per pass: the lists are indexed by layer run)
+            from .state_cache import cache_layers, layer_cache_shapes
 
             k, v = [], []
-            for i in range(self.num_layers):
+            for i in cache_layers(self.model_config):
                 shp = layer_cache_shapes(self.model_config, i, self.num_blocks, self.block_size, self.tp_size)
                 k.append(None if shp is None else torch.zeros(shp[0], dtype=self.kv_cache_dtype, device=self.device))
-                v.append(None if shp is None else torch.zeros(shp[1], dtype=self.kv_cache_dtype, device=self.device))
+                v.append(None if shp is None or shp[1] is None
+                         else torch.zeros(shp[1], dtype=self.kv_cache_dtype, device=self.device))
             return k, v
         shape = (self.num_blocks, self.block_size, self.kv_head_num, self.head_size)
         k = [torch.zeros(shape, dtype=self.kv_cache_dtype, device=self.device) for _ in range(self.num_layers)]

@@ -1,9 +1,12 @@
 """Fixed-size recurrent state per live sequence, beside the paged K / V of attention layers.
 
-A recurrent mixer (linear attention, delta rule) keeps, per sequence, an fp32 matrix per head and - where it has short
-convolutions - the last few inputs of every convolved channel.  The pool holds `max_batch_size` slots per such layer; a
-sequence takes a slot when it is admitted and gives it back when it ends.  Slots are not cleared: the kernels take the
-state of a sequence that has consumed no token yet as zero.
+A recurrent mixer (linear attention, retention, delta rule) keeps, per sequence, an fp32 matrix per head and - where it
+has short convolutions - the last few inputs of every convolved channel.  The pool holds `max_batch_size` slots per such
+layer; a sequence takes a slot when it is admitted and gives it back when it ends.  Slots are not cleared: the kernels
+take the state of a sequence that has consumed no token yet as zero.
+
+Caches and states are indexed by LAYER RUN (`cache_layers`): a layer inside a looped span runs several times per forward
+with the same weights, and every pass owns pages / slots of its own.
 """
 from __future__ import annotations
 
@@ -13,7 +16,15 @@ import torch
 
 from ...accelerator import get_accelerator
 
-__all__ = ["StateCacheManager", "layer_cache_shapes", "layer_state_shapes"]
+__all__ = ["StateCacheManager", "layer_cache_shapes", "layer_state_shapes", "cache_layers"]
+
+
+def cache_layers(model_config) -> List[int]:
+    """Layer index of every layer run, in execution order (one cache / state per run)."""
+    runs = getattr(model_config, "layer_runs", None)
+    if runs is None:
+        return list(range(model_config.num_hidden_layers))
+    return [layer for layer, _ in runs()]
 
 
 def _spec(model_config, layer: int):
@@ -22,13 +33,16 @@ def _spec(model_config, layer: int):
 
 
 def layer_cache_shapes(model_config, layer: int, num_blocks: int, block_size: int,
-                       tp_size: int = 1) -> Optional[Tuple[Tuple[int, ...], Tuple[int, ...]]]:
-    """(K shape, V shape) of a layer's paged cache, None for a layer without one."""
+                       tp_size: int = 1) -> Optional[Tuple[Tuple[int, ...], Optional[Tuple[int, ...]]]]:
+    """(K shape, V shape) of a layer's paged cache, None for a layer without one.  Latent attention keeps ONE row per
+    token, [latent | rotated key part]; its values are the latent columns of the same row (V shape None)."""
     sp = _spec(model_config, layer)
     if sp is None:
         kv = max(getattr(model_config, "num_key_value_heads", model_config.num_attention_heads) // tp_size, 1)
         shp = (num_blocks, block_size, kv, model_config.head_dim)
         return shp, shp
+    if sp.kind == "latent":
+        return (num_blocks, block_size, 1, sp.kv_rank + sp.rot_dim), None
     if sp.kind != "attention":
         return None
     return (num_blocks, block_size, sp.kv_heads, sp.dim), (num_blocks, block_size, sp.kv_heads, sp.vdim)
@@ -52,7 +66,7 @@ class StateCacheManager:
         self.dtype = config.dtype
         self._free: List[int] = list(range(self.num_slots))
         self.states: List[Optional[Dict[str, torch.Tensor]]] = []
-        for i in range(model_config.num_hidden_layers):      # models without recurrent layers only use the slot ids
+        for i in cache_layers(model_config):                  # models without recurrent layers only use the slot ids
             shapes = layer_state_shapes(model_config, i, self.num_slots)
             self.states.append(None if shapes is None else {
                 n: torch.zeros(s, dtype=torch.float32 if n == "S" else self.dtype, device=self.device)

@@ -25,6 +25,7 @@ class PagedKVRuntime:
         self.states = states                                  # per layer: recurrent state tensors indexed by slot
         self.ragged = None                                    # ops.mixers.RaggedMeta of the step (ragged steps)
         self.shared: dict = {}                                # tensors one layer lends to later ones within a step
+        self.run_of: dict = {}                                # layer -> cache index of its current run (looped spans)
         self.block_tables: Optional[torch.Tensor] = None      # [bsz, max_blocks] int32 (device)
         self.seq_lens: Optional[torch.Tensor] = None          # [bsz] int32, INCLUDING the tokens of this step
         self.is_prompt = True
@@ -88,8 +89,28 @@ class PagedKVRuntime:
         self.shared = {}
         return self.token_pos.long()
 
+    def bind_run(self, layer_idx: int, run_idx: int) -> None:
+        """The backbone names the layer run that is about to execute: a layer inside a looped span has one cache /
+        state per pass, stored at the run's index."""
+        self.run_of[layer_idx] = run_idx
+
+    def cache_index(self, layer_idx: int) -> int:
+        return self.run_of.get(layer_idx, layer_idx)
+
     def layer_state(self, layer_idx: int) -> dict:
-        return self.states[layer_idx]
+        return self.states[self.cache_index(layer_idx)]
+
+    def attend_latent(self, layer_idx: int, q: torch.Tensor, scale: float, kv_rank: int) -> torch.Tensor:
+        """Latent attention over the layer's pages (rows [latent | rotated key part], written by the caller through
+        `latent_cache`): q [T, H x (kv_rank + rot)] against the whole row, values = the row's first `kv_rank` columns.
+        Returns [T, H x kv_rank]."""
+        from ...ops import mixers as mops
+
+        kc = self.k_caches[self.cache_index(layer_idx)]
+        return mops.paged_bias_attention(q, kc, kc, self.block_tables, self.ragged, scale, vdim=kv_rank)
+
+    def latent_cache(self, layer_idx: int) -> torch.Tensor:
+        return self.k_caches[self.cache_index(layer_idx)]
 
     def attend_ragged(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
                       bias_table=None, bucket_starts=None, sink: bool = False, v_other=None,
@@ -98,7 +119,7 @@ class PagedKVRuntime:
         every step token over positions 0..pos of its sequence.  q [T, H x dim], k [T, G x dim], v [T, G x vdim]."""
         from ...ops import mixers as mops
 
-        kc, vc = self.k_caches[layer_idx], self.v_caches[layer_idx]
+        kc, vc = self.k_caches[self.cache_index(layer_idx)], self.v_caches[self.cache_index(layer_idx)]
         mops.paged_kv_write_mix(k, v, kc, vc, self.block_tables, self.ragged, v_other=v_other, lam=lam)
         return mops.paged_bias_attention(q, kc, vc, self.block_tables, self.ragged, scale, bias_table=bias_table,
                                          bucket_starts=bucket_starts, sink=sink, lut=lut)
@@ -107,14 +128,14 @@ class PagedKVRuntime:
     def scratch(cls, cfg, batch: int, seqlen: int, device, dtype, block_size: int = 16) -> "PagedKVRuntime":
         """Cache pages and state slots for `batch` fresh sequences of `seqlen` tokens, laid out back to back: what a
         forward without a serving engine runs on."""
-        from ..kv_cache.state_cache import layer_cache_shapes, layer_state_shapes
+        from ..kv_cache.state_cache import cache_layers, layer_cache_shapes, layer_state_shapes
 
         per = (seqlen + block_size - 1) // block_size
         ks, vs, states = [], [], []
-        for i in range(cfg.num_hidden_layers):
+        for i in cache_layers(cfg):
             shp = layer_cache_shapes(cfg, i, batch * per, block_size)
             ks.append(None if shp is None else torch.zeros(shp[0], dtype=dtype, device=device))
-            vs.append(None if shp is None else torch.zeros(shp[1], dtype=dtype, device=device))
+            vs.append(None if shp is None or shp[1] is None else torch.zeros(shp[1], dtype=dtype, device=device))
             st = layer_state_shapes(cfg, i, batch)
             states.append(None if st is None else {
                 n: torch.zeros(sh, dtype=torch.float32 if n == "S" else dtype, device=device) for n, sh in st.items()})

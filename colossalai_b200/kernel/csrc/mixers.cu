@@ -15,7 +15,11 @@
 //   cb_state_scan           (prepare + scan) per head a matrix M [dim, vdim]: either M <- a_h M + outer(k, v) with one
 //                           decay per head, or the gated delta rule M <- diag(r) M; e = w (v - M^T k); M <- M + outer(k, e)
 //                           with a decay per key channel; the read-out y = M^T q follows the write
-//   cb_gated_group_rmsnorm  out = o / rms_group(o) * w * sigmoid(gate)
+//   cb_gated_group_rmsnorm  out = o / rms_group(o) * w * sigmoid(gate) (or silu(gate); w optional)
+//   cb_stream_add_norm      x(fp32) += sum of up to four [T, W] addends + a [W] row;  h = cast(rms / layer norm of x)
+//   cb_rotary_half          rotate-half rotary positions from an fp32 [positions, dims] cos|sin table, strided in / out
+//   cb_latent_kv_write      latent attention's cache row: [rms_norm(latent) * w | rotated shared key part]
+//   cb_clamped_glu          g = min(gate, L); u = clamp(up, -L, L); out = g * sigmoid(alpha g) * (u + 1)
 //   cb_rmsnorm_residual     x(fp32) += mult * y / rms(y) * (offset + w);  h = cast(x)
 //   cb_rmsnorm_f32in        out = cast(x / rms(x) * (offset + w)) for an fp32 residual stream
 //   cb_paged_kv_write_mix   K / V rows (different widths allowed) into the paged cache, V optionally blended with another
@@ -194,6 +198,10 @@ struct ScanParams {
   int act_silu;                 // silu on q, k, v when they are loaded
   int unit_qk;                  // q, k divided by sqrt(sum x^2 + unit_eps) per head
   float unit_eps, q_scale;
+  float k_scale;                // k multiplied by this (after the rotation)
+  const float* rot_table;       // [positions, rot_dims] cos | sin per position, or null: no rotary positions
+  int rot_dims;                 // first channels of every q / k head that are rotated (pairs i, i + rot_dims / 2)
+  const int* token_pos;         // [T] position of every token in its sequence
 };
 
 // Two kernels.  `scan_prepare_kernel` is elementwise and fully parallel: activations, unit norms, decays and write
@@ -234,10 +242,24 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(ScanParams p, ScanWor
       wq[i] = qv;
       wk[i] = kv;
     }
-    float rq = p.q_scale, rk = 1.f;
+    if (p.rot_table != nullptr && p.rot_dims > 0) {      // a lane turns whole pairs: both halves are its own afterwards
+      __syncwarp();
+      const int half = p.rot_dims >> 1;
+      const float* cs = p.rot_table + (int64_t)p.token_pos[t] * p.rot_dims;
+      for (int i = lane; i < half; i += 32) {
+        const float c = cs[i], sn = cs[half + i];
+        const float qu = wq[i], qv = wq[i + half], ku = wk[i], kv = wk[i + half];
+        wq[i] = qu * c - qv * sn;
+        wq[i + half] = qv * c + qu * sn;
+        wk[i] = ku * c - kv * sn;
+        wk[i + half] = kv * c + ku * sn;
+      }
+      __syncwarp();
+    }
+    float rq = p.q_scale, rk = p.k_scale;
     if (p.unit_qk) {
       rq = p.q_scale / sqrtf(warp_sum(ssq) + p.unit_eps);
-      rk = 1.f / sqrtf(warp_sum(ssk) + p.unit_eps);
+      rk = p.k_scale / sqrtf(warp_sum(ssk) + p.unit_eps);
     }
     for (int i = lane; i < DK; i += 32) {      // a lane rescales what it wrote itself; the padding is zero
       wq[i] = i < dim ? wq[i] * rq : 0.f;
@@ -425,12 +447,13 @@ int launch_scan(const ScanParams& p, float* work, int64_t tokens, int nseq, cuda
 }
 
 // ------------------------------------------------------------------------------------------------ norms
-// one warp per (token, group): out = o / sqrt(mean_group(o^2) + eps) * w[c % wn] * sigmoid(gate)
+// one warp per (token, group): out = o / sqrt(mean_group(o^2) + eps) * w[c % wn] * act(gate), act = sigmoid or silu;
+// w and gate are optional
 template <typename T>
 __global__ void __launch_bounds__(256) gated_group_rmsnorm_kernel(const float* __restrict__ o, const T* __restrict__ w,
                                                                   int wn, const T* __restrict__ gate, int64_t ldg,
                                                                   T* __restrict__ out, int64_t tokens, int C, int group,
-                                                                  float eps) {
+                                                                  float eps, int gate_silu) {
   const int lane = threadIdx.x & 31;
   const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int ngroups = C / group;
@@ -444,8 +467,12 @@ __global__ void __launch_bounds__(256) gated_group_rmsnorm_kernel(const float* _
   const float r = 1.f / sqrtf(ss / (float)group + eps);
   for (int i = lane; i < group; i += 32) {
     const int c = c0 + i;
-    float y = row[i] * r * to_f32<T>(w[c % wn]);
-    if (gate != nullptr) y *= sigmoid_f(to_f32<T>(gate[t * ldg + c]));
+    float y = row[i] * r;
+    if (w != nullptr) y *= to_f32<T>(w[c % wn]);
+    if (gate != nullptr) {
+      const float gv = to_f32<T>(gate[t * ldg + c]);
+      y *= gate_silu ? silu_f(gv) : sigmoid_f(gv);
+    }
     out[t * C + c] = from_f32<T>(y);
   }
 }
@@ -497,6 +524,161 @@ __global__ void __launch_bounds__(256) rmsnorm_f32in_kernel(const float* __restr
     out[t * W + i] = from_f32<T>(x[t * W + i] * r * (offset + to_f32<T>(w[i])));
 }
 
+// ------------------------------------------------------------------------------------------------ stream sums + norm
+// One CTA per token row of the fp32 residual stream: x += ((a0 + a1) + a2 + a3) + row, the addends in their own dtypes
+// (fp32 or 16-bit), summed among themselves first; then, with NORM = 1 / 2, h = cast(norm(x) * (offset + w)) where the
+// norm is x / sqrt(mean x^2 + eps) or (x - mean) / sqrt(mean (x - mean)^2 + eps).  The row stays in registers between the
+// passes (up to STREAM_ITEMS values per thread; wider rows are re-read from x, which the same thread wrote).
+constexpr int STREAM_THREADS = 256, STREAM_ITEMS = 8;
+
+struct StreamAddend { const void* p; int64_t ld; int dtype; };
+struct StreamArgs {
+  float* x;
+  StreamAddend a[4];
+  const float* row;
+  const void* w;
+  int w_dtype;
+  void* h;
+  int h_dtype;
+  int W, norm;
+  float eps, offset;
+};
+
+CB_DEVICE float load_any(const void* p, int dtype, int64_t i) {
+  if (dtype == CB_F32) return ((const float*)p)[i];
+  if (dtype == CB_BF16) return __bfloat162float(((const __nv_bfloat16*)p)[i]);
+  return __half2float(((const __half*)p)[i]);
+}
+CB_DEVICE void store_any(void* p, int dtype, int64_t i, float v) {
+  if (dtype == CB_F32) ((float*)p)[i] = v;
+  else if (dtype == CB_BF16) ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
+  else ((__half*)p)[i] = __float2half_rn(v);
+}
+
+__global__ void __launch_bounds__(STREAM_THREADS) stream_add_norm_kernel(StreamArgs g) {
+  __shared__ float red[64];
+  const int64_t t = blockIdx.x;
+  const int W = g.W;
+  float* xr = g.x + t * W;
+  float keep[STREAM_ITEMS];
+  float sum[1] = {0.f};
+  int n = 0;
+  for (int i = threadIdx.x; i < W; i += STREAM_THREADS, ++n) {
+    float add = 0.f;
+    bool any = false;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (g.a[j].p != nullptr) {
+        const float v = load_any(g.a[j].p, g.a[j].dtype, t * g.a[j].ld + i);
+        add = any ? add + v : v;
+        any = true;
+      }
+    if (g.row != nullptr) { add = any ? add + g.row[i] : g.row[i]; any = true; }
+    float xv = xr[i];
+    if (any) { xv += add; xr[i] = xv; }
+    if (n < STREAM_ITEMS) keep[n] = xv;
+    sum[0] += g.norm == 1 ? xv * xv : xv;
+  }
+  if (g.norm == 0) return;
+  block_sum<1>(sum, red);
+  float mean = 0.f, r;
+  if (g.norm == 1) {
+    r = 1.f / sqrtf(sum[0] / (float)W + g.eps);
+  } else {
+    mean = sum[0] / (float)W;
+    float sq[1] = {0.f};
+    n = 0;
+    for (int i = threadIdx.x; i < W; i += STREAM_THREADS, ++n) {
+      const float d = (n < STREAM_ITEMS ? keep[n] : xr[i]) - mean;
+      sq[0] = fmaf(d, d, sq[0]);
+    }
+    block_sum<1>(sq, red);
+    r = 1.f / sqrtf(sq[0] / (float)W + g.eps);
+  }
+  n = 0;
+  for (int i = threadIdx.x; i < W; i += STREAM_THREADS, ++n) {
+    const float xv = n < STREAM_ITEMS ? keep[n] : xr[i];
+    const float wv = g.offset + (g.w != nullptr ? load_any(g.w, g.w_dtype, i) : 1.f);
+    store_any(g.h, g.h_dtype, t * W + i, (xv - mean) * r * wv);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ rotary positions
+// table [positions, dims] fp32: cos(p f_i) for i < dims / 2, then sin(p f_i).  One thread per (token, head, channel of
+// the copied width): channel i < dims / 2 pairs with i + dims / 2; channels at dims and above are copied.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) rotary_half_kernel(const TI* __restrict__ src, int64_t lds, TO* __restrict__ dst,
+                                                          int64_t ldd, int64_t tokens, int heads, int src_hs, int src_off,
+                                                          int dst_hs, int dst_off, int width, int dims,
+                                                          const float* __restrict__ table,
+                                                          const int* __restrict__ token_pos) {
+  const int64_t total = tokens * heads * width;
+  const int half = dims >> 1;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(idx % width);
+    const int h = (int)((idx / width) % heads);
+    const int64_t t = idx / ((int64_t)width * heads);
+    const TI* s = src + t * lds + h * src_hs + src_off;
+    float y = to_f32<TI>(s[c]);
+    if (c < dims) {
+      const float* cs = table + (int64_t)token_pos[t] * dims;
+      const int i = c < half ? c : c - half;
+      const float co = cs[i], sn = cs[half + i];
+      const float other = to_f32<TI>(s[c < half ? c + half : c - half]);
+      y = c < half ? y * co - other * sn : y * co + other * sn;
+    }
+    dst[t * ldd + h * dst_hs + dst_off + c] = from_f32<TO>(y);
+  }
+}
+
+// One warp per token: the first `rank` columns of z are RMS-normalised with weight w (the latent), the last `rot` are
+// turned by the token's position; both go into the token's row of the paged cache [blocks, block_size, 1, rank + rot].
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128) latent_kv_write_kernel(const T* __restrict__ z, int64_t ldz, const TW* __restrict__ w,
+                                                              float eps, int rank, int rot,
+                                                              const float* __restrict__ table, T* __restrict__ cache,
+                                                              const int* __restrict__ block_tables,
+                                                              const int* __restrict__ token_seq,
+                                                              const int* __restrict__ token_pos, int64_t tokens,
+                                                              int block_size, int max_blocks) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  const int seq = token_seq[t], pos = token_pos[t];
+  const int64_t row = (int64_t)block_tables[(int64_t)seq * max_blocks + pos / block_size] * block_size + pos % block_size;
+  const T* zr = z + t * ldz;
+  T* out = cache + row * (rank + rot);
+  float ss = 0.f;
+  for (int i = lane; i < rank; i += 32) { const float v = to_f32<T>(zr[i]); ss = fmaf(v, v, ss); }
+  ss = warp_sum(ss);
+  const float r = 1.f / sqrtf(ss / (float)rank + eps);
+  for (int i = lane; i < rank; i += 32) out[i] = from_f32<T>(to_f32<T>(zr[i]) * r * to_f32<TW>(w[i]));
+  const int half = rot >> 1;
+  const float* cs = table + (int64_t)pos * rot;
+  for (int i = lane; i < half; i += 32) {
+    const float u = to_f32<T>(zr[rank + i]), v = to_f32<T>(zr[rank + half + i]);
+    const float c = cs[i], sn = cs[half + i];
+    out[rank + i] = from_f32<T>(u * c - v * sn);
+    out[rank + half + i] = from_f32<T>(v * c + u * sn);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ clamped gated unit
+// gu [rows, 2 I] = gate | up.  IEEE fp32 arithmetic (this file is built without fast math), one rounding into T.
+template <typename T>
+__global__ void __launch_bounds__(256) clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t rows, int I,
+                                                          float limit, float alpha, const int64_t* __restrict__ row_limit) {
+  if (row_limit != nullptr) rows = min(rows, *row_limit);
+  const int64_t total = rows * I;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / I;
+    const int c = (int)(idx - r * I);
+    const float gq = fminf(to_f32<T>(gu[r * 2 * I + c]), limit);
+    const float u = fminf(fmaxf(to_f32<T>(gu[r * 2 * I + I + c]), -limit), limit);
+    out[idx] = from_f32<T>(gq * sigmoid_f(alpha * gq) * (u + 1.f));
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ paged cache write
 template <typename T>
 __global__ void __launch_bounds__(128) paged_kv_write_mix_kernel(const T* __restrict__ k, int64_t ldk, const T* __restrict__ v,
@@ -523,14 +705,15 @@ __global__ void __launch_bounds__(128) paged_kv_write_mix_kernel(const T* __rest
 // One warp per (step token, query head).  Keys 0..pos of the token's sequence are walked in tiles of 32 in a fixed order
 // (lane = key for the scores, lane = value channel for the weighted sum), online softmax in fp32.  With `sink` the running
 // maximum starts at 0 and the denominator at 1: a key of score 0 without a value.
-constexpr int ATT_MAX_VREG = 8;   // value width up to 256
+constexpr int ATT_MAX_VREG = 16;  // value width up to 512
 
 template <typename T>
 __global__ void __launch_bounds__(128) paged_bias_attention_kernel(
     const T* __restrict__ q, int64_t ldq, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
     const float* __restrict__ bias_table, const int* __restrict__ bucket_start, int nbuckets, T* __restrict__ out,
-    int64_t tokens, int heads, int kv_heads, int dim, int vdim, int block_size, int max_blocks, float scale, int sink) {
+    int64_t tokens, int heads, int kv_heads, int dim, int vdim, int ldv, int block_size, int max_blocks, float scale,
+    int sink) {
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   float* qs = smem + warp * dim;
@@ -587,7 +770,7 @@ __global__ void __launch_bounds__(128) paged_bias_attention_kernel(
     for (int jj = 0; jj < nk; ++jj) {
       const float pw = __shfl_sync(0xffffffffu, pj, jj);
       const int64_t vrow = __shfl_sync(0xffffffffu, myrow, jj);
-      const T* vr = v_cache + vrow * vdim;
+      const T* vr = v_cache + vrow * ldv;      // ldv = vdim, or the key row's width when the values live in the key rows
 #pragma unroll
       for (int r = 0; r < ATT_MAX_VREG; ++r) {
         const int c = lane + 32 * r;
@@ -658,7 +841,7 @@ __global__ void __launch_bounds__(128, MT == 2 ? 2 : 3) paged_bias_attention_mma
     const T* __restrict__ q, int64_t ldq, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const float* __restrict__ bias_table, const uint8_t* __restrict__ lut, int lut_n, int nbuckets, T* __restrict__ out,
-    int heads, int kv_heads, int dim, int vdim, int block_size, int max_blocks, float scale, int sink, int chunk,
+    int heads, int kv_heads, int dim, int vdim, int ldv, int block_size, int max_blocks, float scale, int sink, int chunk,
     int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
   constexpr int BM = 64 * MT;
   constexpr int LDS = D + 8;                    // padded row: 16-byte aligned, conflict-free fragment reads
@@ -683,6 +866,8 @@ __global__ void __launch_bounds__(128, MT == 2 ? 2 : 3) paged_bias_attention_mma
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
   for (int i = tid; i < nbuckets * R; i += 128) tab[i] = bias_table[(i / R) * heads + g * R + (i % R)] * LOG2E;
   const int* bt = block_tables + (int64_t)s * max_blocks;
+  // values that live in the key rows (latent attention: value = the row's first vdim columns): the K tile serves as V
+  const bool kv_same = v_cache == k_cache && ldv == dim;
 
   auto load_tile = [&](int stage, int j0) {
     constexpr int CH = D / 8;
@@ -695,7 +880,7 @@ __global__ void __launch_bounds__(128, MT == 2 ? 2 : 3) paged_bias_attention_mma
       const int64_t row = in ? ((int64_t)bt[j / block_size] * block_size + j % block_size) * kv_heads + g : 0;
       const bool kin = in && c8 < dim, vin = in && c8 < vdim;
       cp_async16(Ks + r * LDS + c8, k_cache + (kin ? row * dim + c8 : 0), kin ? 16u : 0u);
-      cp_async16(Vs + r * LDS + c8, v_cache + (vin ? row * vdim + c8 : 0), vin ? 16u : 0u);
+      if (!kv_same) cp_async16(Vs + r * LDS + c8, v_cache + (vin ? row * ldv + c8 : 0), vin ? 16u : 0u);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -752,7 +937,7 @@ __global__ void __launch_bounds__(128, MT == 2 ? 2 : 3) paged_bias_attention_mma
     __syncthreads();
     if (j0 <= whi) {                            // warp-uniform: otherwise the whole tile is masked for this warp
       const T* Ks = KV + stage * 2 * TILE;
-      const T* Vs = Ks + TILE;
+      const T* Vs = kv_same ? Ks : Ks + TILE;
       float sacc[MT][MMA_BN / 8][4];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
@@ -944,8 +1129,8 @@ template <typename T, int D, int MT>
 int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
                          const int* cu_q, const int* ctx_len, const int* token_pos, const float* bias_table,
                          const uint8_t* lut, int lut_n, int nbuckets, void* out, int64_t tokens, int nseq, int max_q,
-                         int heads, int kv_heads, int dim, int vdim, int block_size, int max_blocks, float scale, int sink,
-                         int chunk, int max_splits, float* part_o, float* part_ml, cudaStream_t st) {
+                         int heads, int kv_heads, int dim, int vdim, int ldv, int block_size, int max_blocks, float scale,
+                         int sink, int chunk, int max_splits, float* part_o, float* part_ml, cudaStream_t st) {
   const int R = heads / kv_heads;
   constexpr int BM = 64 * MT;
   const size_t smem = (size_t)(4 * MMA_BN + BM) * (D + 8) * sizeof(T) + (size_t)nbuckets * R * sizeof(float);
@@ -960,7 +1145,7 @@ int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const 
   const int rowtiles = (max_q * R + BM - 1) / BM;
   dim3 grid(rowtiles * (chunk > 0 ? max_splits : 1), kv_heads, nseq);
   kern<<<grid, 128, smem, st>>>((const T*)q, ldq, (const T*)k_cache, (const T*)v_cache, block_tables, cu_q, ctx_len,
-                                bias_table, lut, lut_n, nbuckets, (T*)out, heads, kv_heads, dim, vdim, block_size,
+                                bias_table, lut, lut_n, nbuckets, (T*)out, heads, kv_heads, dim, vdim, ldv, block_size,
                                 max_blocks, scale, sink, chunk, max_splits, part_o, part_ml);
   if (chunk > 0) {
     const int64_t units = tokens * heads;
@@ -1012,11 +1197,12 @@ int cb_state_scan(int mode, const void* q, int64_t ldq, const void* k, int64_t l
                   const void* araw, int64_t lda, const void* braw, int64_t ldb, const float* head_decay,
                   const float* a_log, const float* dt_bias, float* state, float* out, float* work, int64_t tokens,
                   const int* cu_q, const int* ctx_len, const int* slots, int nseq, int heads, int qk_heads, int dim,
-                  int vdim, int act_silu, int unit_qk, float unit_eps, float q_scale, int dtype, cudaStream_t st) {
+                  int vdim, int act_silu, int unit_qk, float unit_eps, float q_scale, float k_scale,
+                  const float* rot_table, int rot_dims, const int* token_pos, int dtype, cudaStream_t st) {
   if (nseq == 0 || tokens == 0) return 0;
-  if (heads % qk_heads != 0) return (int)cudaErrorInvalidValue;
+  if (heads % qk_heads != 0 || rot_dims > dim || (rot_dims & 1)) return (int)cudaErrorInvalidValue;
   ScanParams p{q, k, v, ldq, ldk, ldv, araw, lda, braw, ldb, head_decay, a_log, dt_bias, state, out, cu_q, ctx_len, slots,
-               heads, qk_heads, dim, vdim, act_silu, unit_qk, unit_eps, q_scale};
+               heads, qk_heads, dim, vdim, act_silu, unit_qk, unit_eps, q_scale, k_scale, rot_table, rot_dims, token_pos};
   CB_DISPATCH_FLOAT(dtype, T, {
     if (mode == SCAN_DELTA) return launch_scan<SCAN_DELTA, T>(p, work, tokens, nseq, st);
     return launch_scan<SCAN_DECAY, T>(p, work, tokens, nseq, st);
@@ -1025,13 +1211,13 @@ int cb_state_scan(int mode, const void* q, int64_t ldq, const void* k, int64_t l
 }
 
 int cb_gated_group_rmsnorm(const float* o, const void* w, int wn, const void* gate, int64_t ldg, void* out, int64_t tokens,
-                           int C, int group, float eps, int dtype, cudaStream_t st) {
+                           int C, int group, float eps, int gate_silu, int dtype, cudaStream_t st) {
   if (tokens == 0) return 0;
   if (group <= 0 || C % group != 0) return (int)cudaErrorInvalidValue;
   const int64_t units = tokens * (C / group);
   CB_DISPATCH_FLOAT(dtype, T, {
     gated_group_rmsnorm_kernel<T><<<(unsigned)((units + 7) / 8), 256, 0, st>>>(o, (const T*)w, wn, (const T*)gate, ldg,
-                                                                              (T*)out, tokens, C, group, eps);
+                                                                              (T*)out, tokens, C, group, eps, gate_silu);
   });
   return CB_LAUNCH_CHECK();
 }
@@ -1061,6 +1247,63 @@ int cb_rmsnorm_f32in(const float* x, const void* w, void* out, int64_t tokens, i
   return CB_LAUNCH_CHECK();
 }
 
+int cb_stream_add_norm(float* x, const void* a0, int64_t ld0, int dt0, const void* a1, int64_t ld1, int dt1, const void* a2,
+                       int64_t ld2, int dt2, const void* a3, int64_t ld3, int dt3, const float* row, const void* w,
+                       int w_dtype, void* h, int h_dtype, int64_t tokens, int W, int norm, float eps, float offset,
+                       cudaStream_t st) {
+  if (tokens == 0) return 0;
+  if (norm < 0 || norm > 2 || (norm != 0 && h == nullptr)) return (int)cudaErrorInvalidValue;
+  StreamArgs g{x, {{a0, ld0, dt0}, {a1, ld1, dt1}, {a2, ld2, dt2}, {a3, ld3, dt3}}, row, w, w_dtype, h, h_dtype, W, norm,
+               eps, offset};
+  stream_add_norm_kernel<<<(unsigned)tokens, STREAM_THREADS, 0, st>>>(g);
+  return CB_LAUNCH_CHECK();
+}
+
+int cb_rotary_half(const void* src, int64_t lds, void* dst, int64_t ldd, int64_t tokens, int heads, int src_hs, int src_off,
+                   int dst_hs, int dst_off, int width, int dims, const float* table, const int* token_pos, int src_dtype,
+                   int dst_dtype, cudaStream_t st) {
+  if (tokens == 0 || heads == 0 || width == 0) return 0;
+  if (dims > width || (dims & 1) || src_dtype != dst_dtype) return (int)cudaErrorInvalidValue;
+  const int64_t total = tokens * heads * width;
+  const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  CB_DISPATCH_FLOAT(src_dtype, T, {
+    rotary_half_kernel<T, T><<<grid, 256, 0, st>>>((const T*)src, lds, (T*)dst, ldd, tokens, heads, src_hs, src_off, dst_hs,
+                                                   dst_off, width, dims, table, token_pos);
+  });
+  return CB_LAUNCH_CHECK();
+}
+
+int cb_latent_kv_write(const void* z, int64_t ldz, const void* w, int w_dtype, float eps, int rank, int rot,
+                       const float* table, void* cache, const int* block_tables, const int* token_seq, const int* token_pos,
+                       int64_t tokens, int block_size, int max_blocks, int dtype, cudaStream_t st) {
+  if (tokens == 0) return 0;
+  if (rot & 1) return (int)cudaErrorInvalidValue;
+  const unsigned grid = (unsigned)((tokens + 3) / 4);
+  CB_DISPATCH_FLOAT(dtype, T, {
+    if (w_dtype == CB_F32)
+      latent_kv_write_kernel<T, float><<<grid, 128, 0, st>>>((const T*)z, ldz, (const float*)w, eps, rank, rot, table,
+                                                             (T*)cache, block_tables, token_seq, token_pos, tokens,
+                                                             block_size, max_blocks);
+    else if (w_dtype == dtype)
+      latent_kv_write_kernel<T, T><<<grid, 128, 0, st>>>((const T*)z, ldz, (const T*)w, eps, rank, rot, table, (T*)cache,
+                                                         block_tables, token_seq, token_pos, tokens, block_size, max_blocks);
+    else
+      return (int)cudaErrorInvalidValue;
+  });
+  return CB_LAUNCH_CHECK();
+}
+
+int cb_clamped_glu(const void* gu, void* out, int64_t rows, int I, float limit, float alpha, int dtype,
+                   const int64_t* row_limit, cudaStream_t st) {
+  if (rows == 0 || I == 0) return 0;
+  const int64_t total = rows * I;
+  const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  CB_DISPATCH_FLOAT(dtype, T, {
+    clamped_glu_kernel<T><<<grid, 256, 0, st>>>((const T*)gu, (T*)out, rows, I, limit, alpha, row_limit);
+  });
+  return CB_LAUNCH_CHECK();
+}
+
 int cb_paged_kv_write_mix(const void* k, int64_t ldk, const void* v, int64_t ldv, const void* v_other, int64_t ldvo,
                           float lam, void* k_cache, void* v_cache, const int* block_tables, const int* token_seq,
                           const int* token_pos, int64_t tokens, int kw, int vw, int block_size, int max_blocks, int dtype,
@@ -1076,7 +1319,7 @@ int cb_paged_kv_write_mix(const void* k, int64_t ldk, const void* v, int64_t ldv
 
 int cb_paged_bias_attention(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
                             const int* token_seq, const int* token_pos, const float* bias_table, const int* bucket_start,
-                            int nbuckets, void* out, int64_t tokens, int heads, int kv_heads, int dim, int vdim,
+                            int nbuckets, void* out, int64_t tokens, int heads, int kv_heads, int dim, int vdim, int ldv,
                             int block_size, int max_blocks, float scale, int sink, int dtype, cudaStream_t st) {
   if (tokens == 0) return 0;
   if (vdim > 32 * ATT_MAX_VREG || heads % kv_heads != 0) return (int)cudaErrorInvalidValue;
@@ -1086,7 +1329,7 @@ int cb_paged_bias_attention(const void* q, int64_t ldq, const void* k_cache, con
   CB_DISPATCH_FLOAT(dtype, T, {
     paged_bias_attention_kernel<T><<<(unsigned)((units + nwarps - 1) / nwarps), nwarps * 32, smem, st>>>(
         (const T*)q, ldq, (const T*)k_cache, (const T*)v_cache, block_tables, token_seq, token_pos, bias_table,
-        bucket_start, nbuckets, (T*)out, tokens, heads, kv_heads, dim, vdim, block_size, max_blocks, scale, sink);
+        bucket_start, nbuckets, (T*)out, tokens, heads, kv_heads, dim, vdim, ldv, block_size, max_blocks, scale, sink);
   });
   return CB_LAUNCH_CHECK();
 }
@@ -1096,11 +1339,12 @@ int cb_paged_bias_attention(const void* q, int64_t ldq, const void* k_cache, con
 int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
                                 const int* block_tables, const int* cu_q, const int* ctx_len, const int* token_pos,
                                 const float* bias_table, const uint8_t* lut, int lut_n, int nbuckets, void* out,
-                                int64_t tokens, int nseq, int max_q, int heads, int kv_heads, int dim, int vdim,
+                                int64_t tokens, int nseq, int max_q, int heads, int kv_heads, int dim, int vdim, int ldv,
                                 int block_size, int max_blocks, float scale, int sink, int chunk, int max_splits,
                                 float* part_o, float* part_ml, int dtype, cudaStream_t st) {
   if (nseq == 0 || max_q == 0) return 0;
   if (heads % kv_heads != 0 || dim % 8 != 0 || vdim % 8 != 0 || dim > 128 || vdim > 128 || (ldq & 7) || ((uintptr_t)q & 15) ||
+      (ldv & 7) || ldv < vdim ||
       chunk % MMA_BN != 0)
     return (int)cudaErrorInvalidValue;
   const int dmax = dim > vdim ? dim : vdim;
@@ -1109,10 +1353,11 @@ int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache,
   if (wide)                                                                                                           \
     return launch_attention_mma<T, D, 2>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table, \
                                          lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,  \
-                                         block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, st); \
+                                         ldv, block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, \
+                                         st);                                                                         \
   return launch_attention_mma<T, D, 1>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table,  \
                                        lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,   \
-                                       block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, st)
+                                       ldv, block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, st)
   CB_DISPATCH_HALF(dtype, T, {
     if (dmax <= 32) { CB_ATT_MMA(T, 32); }
     else if (dmax <= 64) { CB_ATT_MMA(T, 64); }

@@ -420,6 +420,21 @@ inline EpParams make_ep(const void* const* rows, const void* const* flags, const
   return p;
 }
 
+// out[t] = sum_j w[t, j] * rows[row_of[t, j]] in fp32, j ascending (a fixed order per token: no atomics).  One CTA per
+// token; rows in any float dtype.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_gather_combine_kernel(const T* __restrict__ rows, const int64_t* __restrict__ row_of,
+                                                                 const float* __restrict__ w, float* __restrict__ out,
+                                                                 int k, int H) {
+  const int64_t t = blockIdx.x;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < k; ++j)
+      acc = fmaf(w[t * k + j], to_f32<T>(rows[row_of[t * k + j] * H + c]), acc);
+    out[t * H + c] = acc;
+  }
+}
+
 }  // namespace
 
 // Copy the live part of a receive buffer into an autograd-owned tensor: rows of the padded local layout that hold a
@@ -578,6 +593,15 @@ int cb_moe_ep_combine(const int* topk_idx, const float* w, const int* pos, const
   if (grid < 1) grid = 1;
   CB_DISPATCH_HALF(dtype, T, {
     ep_pull_combine_kernel<T><<<grid, 256, 0, st>>>(p, topk_idx, w, pos, (T*)out, (T*)ys_keep, tokens, K, H);
+  });
+  return CB_LAUNCH_CHECK();
+}
+
+int cb_moe_gather_combine(const void* rows, const int64_t* row_of, const float* w, float* out, int tokens, int k, int H,
+                          int dtype, cudaStream_t st) {
+  if (tokens == 0) return 0;
+  CB_DISPATCH_FLOAT(dtype, T, {
+    moe_gather_combine_kernel<T><<<(unsigned)tokens, 256, 0, st>>>((const T*)rows, row_of, w, out, k, H);
   });
   return CB_LAUNCH_CHECK();
 }

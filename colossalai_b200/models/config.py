@@ -6,9 +6,9 @@ HF config fields the reference's policies read (`shardformer/policies/*.py`).
 from __future__ import annotations
 
 from dataclasses import asdict, dataclass, field, replace
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, List, Optional, Tuple
 
-__all__ = ["ModelConfig", "MoEConfig", "MixerSpec", "LayerSpec", "MODEL_ZOO", "get_config"]
+__all__ = ["ModelConfig", "MoEConfig", "MixerSpec", "ExpertFFSpec", "LayerSpec", "MODEL_ZOO", "get_config"]
 
 
 @dataclass
@@ -40,7 +40,13 @@ class MixerSpec:
                        first `v_mix` layer.
     kind "lightning":  per-head outer-product memory with one scalar `decay` per head, read out by q.
     kind "channel_delta": gated delta rule with a decay per head and key channel, short causal convolutions of `conv`
-                       taps on q, k, v, low-rank (`decay_rank`, `gate_rank`) projections for the decay and output gate."""
+                       taps on q, k, v, low-rank (`decay_rank`, `gate_rank`) projections for the decay and output gate.
+    kind "latent":     softmax attention whose keys and values are rebuilt from one `kv_rank`-wide normalised latent per
+                       token plus one `rot_dim`-wide rotated key part shared by all heads; q heads are `dim` unrotated +
+                       `rot_dim` rotated channels; only the latent and the rotated part are cached.
+    kind "retention":  outer-product memory per head with one scalar `decay` per head, rotary positions on the first
+                       `rot_dims` channels of q and k (base `rot_base`), k scaled by dim^-1/2, no softmax; the read-out
+                       is brought to unit RMS per head and gated."""
 
     kind: str = "attention"
     heads: int = 1
@@ -58,6 +64,10 @@ class MixerSpec:
     conv: int = 0
     decay_rank: int = 0
     gate_rank: int = 0
+    kv_rank: int = 0
+    rot_dim: int = 0                  # width of the decoupled rotated q / k part (latent attention)
+    rot_dims: int = 0                 # channels of a head that rotary positions turn (rotate-half pairs)
+    rot_base: float = 10000.0
 
     def __post_init__(self) -> None:
         if self.kv_heads is None:
@@ -68,17 +78,39 @@ class MixerSpec:
 
     @property
     def recurrent(self) -> bool:
-        return self.kind != "attention"
+        return self.kind in ("lightning", "channel_delta", "retention")
+
+    @property
+    def paged(self) -> bool:
+        return self.kind in ("attention", "latent")
+
+
+@dataclass
+class ExpertFFSpec:
+    """Routed feed-forward of one layer: `experts` gated experts of width `ff`, every token uses the `top` of largest
+    softmax score (weights renormalised to one), plus an optional shared expert of width `shared_ff` for every token.
+    Expert activation: g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1)."""
+
+    experts: int = 1
+    top: int = 1
+    ff: int = 0
+    limit: float = 7.0
+    alpha: float = 1.702
+    shared_ff: int = 0
+    shared_limit: float = 7.0
 
 
 @dataclass
 class LayerSpec:
     mixer: MixerSpec = field(default_factory=MixerSpec)
-    ff: Optional[int] = None          # feed-forward width; None = the layer has no feed-forward
+    ff: Optional[int] = None          # dense feed-forward width; None = no dense feed-forward
+    moe: Optional[ExpertFFSpec] = None  # routed feed-forward instead of a dense one
 
     def __post_init__(self) -> None:
         if isinstance(self.mixer, dict):
             self.mixer = MixerSpec(**self.mixer)
+        if isinstance(self.moe, dict):
+            self.moe = ExpertFFSpec(**self.moe)
 
 
 @dataclass
@@ -133,6 +165,14 @@ class ModelConfig:
     residual_mult: float = 1.0
     norm_weight_offset: float = 0.0   # zero-centred norm weights: the norm multiplies by (offset + w)
     fp32_residual: bool = False       # the residual stream stays in fp32 whatever the compute dtype
+    norm_bias: bool = True            # layer norms carry a bias
+    logit_softcap: Optional[float] = None   # logits <- cap * tanh(logits / cap), after `logit_scale`
+    # looped span: layers loop_start .. loop_stop-1 run `loop_times` times in a row with the same weights; every pass
+    # has caches / states of its own and starts by adding the embedding output (not the first pass) and a learned
+    # vector of the pass to the stream
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
     pad_token_id: Optional[int] = None
     bos_token_id: int = 1
     eos_token_id: int = 2
@@ -141,7 +181,7 @@ class ModelConfig:
         if self.layer_specs is not None:
             self.layer_specs = [LayerSpec(**s) if isinstance(s, dict) else s for s in self.layer_specs]
             self.num_hidden_layers = len(self.layer_specs)
-            att = [s.mixer for s in self.layer_specs if s.mixer.kind == "attention"] or [self.layer_specs[0].mixer]
+            att = [s.mixer for s in self.layer_specs if s.mixer.paged] or [self.layer_specs[0].mixer]
             self.num_attention_heads, self.num_key_value_heads, self.head_dim = att[0].heads, att[0].kv_heads, att[0].dim
         if self.num_key_value_heads is None:
             self.num_key_value_heads = self.num_attention_heads
@@ -156,6 +196,24 @@ class ModelConfig:
             self.attention_out_bias = self.attention_bias
         if isinstance(self.moe, dict):
             self.moe = MoEConfig(**self.moe)
+
+    @property
+    def looped(self) -> bool:
+        return self.loop_stop > self.loop_start
+
+    def layer_runs(self) -> List[Tuple[int, Optional[int]]]:
+        """(layer, pass) in execution order; pass is None outside the looped span.  The index into this list is the
+        layer run's cache index: a layer of the span owns one cache / state per pass."""
+        n = self.num_hidden_layers
+        if not self.looped:
+            return [(i, None) for i in range(n)]
+        a, b = self.loop_start, self.loop_stop
+        return [(i, None) for i in range(a)] + [(i, t) for t in range(self.loop_times) for i in range(a, b)] + \
+            [(i, None) for i in range(b, n)]
+
+    @property
+    def num_cache_layers(self) -> int:
+        return len(self.layer_runs())
 
     @property
     def q_size(self) -> int:

@@ -33,6 +33,10 @@ def config_from_hf(hf: dict) -> ModelConfig:
         from .gopunex import gopunex_config
 
         return gopunex_config(hf)
+    if hf.get("architecture") == "Palilix":
+        from .palilix import palilix_config
+
+        return palilix_config(hf)
     if mt == "gpt2":
         return ModelConfig(model_type="gpt2", vocab_size=hf["vocab_size"], hidden_size=hf["n_embd"],
                            intermediate_size=hf.get("n_inner") or 4 * hf["n_embd"], num_hidden_layers=hf["n_layer"],
@@ -480,6 +484,10 @@ def load_hf_checkpoint(path: str, dtype: torch.dtype = torch.bfloat16, device: s
         from .gopunex import load_gopunex
 
         return load_gopunex(path, hf_cfg, dtype, device)
+    if hf_cfg.get("architecture") == "Palilix":
+        from .palilix import load_palilix
+
+        return load_palilix(path, hf_cfg, dtype, device)
     cfg = config_from_hf(hf_cfg)
     model = build_model(cfg).to(dtype)
     merged: Dict[str, torch.Tensor] = {}

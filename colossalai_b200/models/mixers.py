@@ -4,7 +4,10 @@
     zero-score sink in the denominator, an RMS norm over the whole q / k projection and a blend of the values with
     those of the first value-mixing layer;
   * `LightningAttention`: linear attention with one scalar decay per head (an outer-product memory per head);
-  * `ChannelDeltaMixer`: gated delta rule with a decay per head and key channel and short causal convolutions.
+  * `ChannelDeltaMixer`: gated delta rule with a decay per head and key channel and short causal convolutions;
+  * `LatentAttention`: softmax attention whose keys / values are rebuilt from one small normalised latent per token plus
+    one rotated key part shared by all heads - only those are cached, and the attention runs in the latent space;
+  * `Retention`: decayed outer-product memory per head with rotary positions on q / k, no softmax, unit-RMS gated read-out.
 
 Every mixer keeps the call signature of `Attention` (`forward(x, meta, rope, kv_cache)`) and is selected per layer by
 `ModelConfig.layer_specs[i].mixer.kind` (`build_mixer`).  `kv_cache` is the step runtime (`inference.modeling.PagedKVRuntime`):
@@ -23,7 +26,7 @@ from .. import ops
 from ..ops import mixers as mops
 from .config import MixerSpec, ModelConfig
 
-__all__ = ["BiasSinkAttention", "LightningAttention", "ChannelDeltaMixer", "build_mixer"]
+__all__ = ["BiasSinkAttention", "LightningAttention", "ChannelDeltaMixer", "LatentAttention", "Retention", "build_mixer"]
 
 
 class _MixerBase(nn.Module):
@@ -142,7 +145,77 @@ class ChannelDeltaMixer(_MixerBase):
         return self.o_proj(o)
 
 
-_KINDS = {"attention": BiasSinkAttention, "lightning": LightningAttention, "channel_delta": ChannelDeltaMixer}
+class LatentAttention(_MixerBase):
+    """q = W_q h, per head [dim unrotated | rot_dim rotated]; W_dkv h = [kv_rank latent | rot_dim key part]; the latent is
+    RMS-normalised (weight `dkv_norm_weight`) -> c, the key part is rotated -> k_r (one for all heads).  Head n scores
+    position j with scale * (q_n . (U_n c_j) + q_r . k_r_j) and mixes the values V_n c_j.
+
+    The cache holds one row [c | k_r] per token.  Both up-projections are absorbed into the query / output side:
+    q_n . (U_n c) = (U_n^T q_n) . c, and sum_j p_j V_n c_j = V_n (sum_j p_j c_j), so the step runs multi-query attention
+    with queries [U_n^T q_n | rotated q_r] against the cached rows, values = the rows' latent columns, and maps the
+    `kv_rank`-wide results through V_n afterwards (two batched GEMMs over the heads).  A prompt, a portion and a decoded
+    token take the same path, so a position's result does not depend on how the prompt was cut."""
+
+    def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
+        super().__init__(cfg, spec, layer_idx)
+        H, d, r, dv, R = spec.heads, spec.dim, spec.rot_dim, spec.vdim, spec.kv_rank
+        assert spec.rot_dims in (0, r) and r % 2 == 0, "the decoupled key part is rotated as a whole"
+        self.in_proj = nn.Linear(cfg.hidden_size, H * (d + r) + R + r, bias=False)       # q | latent | key part
+        self.dkv_norm_weight = nn.Parameter(torch.ones(R))
+        self.uk = nn.Parameter(torch.zeros(H, d, R))              # U_n: latent -> unrotated key of head n
+        self.uv = nn.Parameter(torch.zeros(H, dv, R))             # V_n: latent -> value of head n
+        self.o_proj = nn.Linear(H * dv, cfg.hidden_size, bias=False)
+        self.scale = spec.scale if spec.scale is not None else (d + r) ** -0.5
+
+    def forward(self, x: torch.Tensor, meta, rope=None, kv_cache=None) -> torch.Tensor:
+        sp = self.spec
+        H, d, r, dv, R = sp.heads, sp.dim, sp.rot_dim, sp.vdim, sp.kv_rank
+        T = x.shape[0]
+        z = self.in_proj(x)
+        q, dkv = z[:, : H * (d + r)], z[:, H * (d + r):]
+        ragged = kv_cache.ragged
+        table = mops.rotary_table(kv_cache.max_len_host, r, sp.rot_base, x.device)
+        mops.latent_kv_write(dkv, self.dkv_norm_weight, self.cfg.norm_eps, R, table, kv_cache.latent_cache(self.layer_idx),
+                             kv_cache.block_tables, ragged)
+        qa = torch.empty(T, H * (R + r), dtype=x.dtype, device=x.device)
+        qa3 = qa.view(T, H, R + r)
+        torch.bmm(q.view(T, H, d + r)[..., :d].transpose(0, 1), self.uk, out=qa3[..., :R].transpose(0, 1))
+        mops.rotary_half(q, qa, H, d + r, d, R + r, R, r, r, table, ragged.token_pos)
+        o = kv_cache.attend_latent(self.layer_idx, qa, self.scale, R)                  # [T, H x R]
+        o = torch.bmm(o.view(T, H, R).transpose(0, 1), self.uv.transpose(1, 2))        # [H, T, dv]
+        return self.o_proj(o.transpose(0, 1).reshape(T, H * dv))
+
+
+class Retention(_MixerBase):
+    """Per head a matrix S [dim, vdim], zero at the start of a sequence and carried in fp32: S <- decay_n S + outer(k, v),
+    read-out S^T q after the write.  q, k get rotary positions on their first `rot_dims` channels and k the factor
+    dim^-1/2, both in fp32; every head's read-out is divided by its root mean square (no weight), multiplied by
+    silu(W_g h) and projected."""
+
+    def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
+        super().__init__(cfg, spec, layer_idx)
+        H, d, dv = spec.heads, spec.dim, spec.vdim
+        assert spec.decay is not None and len(spec.decay) == H, "one decay per head"
+        assert spec.rot_dims % 2 == 0 and spec.rot_dims <= d
+        self.in_proj = nn.Linear(cfg.hidden_size, 2 * H * d + 2 * H * dv, bias=False)      # q | k | v | gate
+        self.o_proj = nn.Linear(H * dv, cfg.hidden_size, bias=False)
+
+    def forward(self, x: torch.Tensor, meta, rope=None, kv_cache=None) -> torch.Tensor:
+        sp = self.spec
+        H, d, dv = sp.heads, sp.dim, sp.vdim
+        z = self.in_proj(x)
+        q, k, v, g = z.split([H * d, H * d, H * dv, H * dv], dim=-1)
+        decay = self._aux("decay", x.device, lambda: torch.tensor(sp.decay, dtype=torch.float64).float())
+        table = mops.rotary_table(kv_cache.max_len_host, sp.rot_dims, sp.rot_base, x.device) if sp.rot_dims else None
+        st = kv_cache.layer_state(self.layer_idx)
+        o = mops.state_scan_decay(q, k, v, decay, st["S"], kv_cache.ragged, H, d, dv, act_silu=False, rot_table=table,
+                                  rot_dims=sp.rot_dims, k_scale=d ** -0.5)
+        o = mops.gated_group_rms_norm(o, None, g, dv, self.cfg.norm_eps, x.dtype, gate_act="silu")
+        return self.o_proj(o)
+
+
+_KINDS = {"attention": BiasSinkAttention, "lightning": LightningAttention, "channel_delta": ChannelDeltaMixer,
+          "latent": LatentAttention, "retention": Retention}
 
 
 def build_mixer(cfg: ModelConfig, layer_idx: int) -> nn.Module:

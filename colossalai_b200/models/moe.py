@@ -23,7 +23,7 @@ from ..parallel import comm
 from ..tensor.moe_tensor import set_moe_tensor_ep_group
 from .config import ModelConfig
 
-__all__ = ["SparseMoE", "Router", "GroupedExperts"]
+__all__ = ["SparseMoE", "Router", "GroupedExperts", "ClampedGLU", "ClampedExpertFF"]
 
 
 class Router(nn.Module):
@@ -64,11 +64,14 @@ class Router(nn.Module):
 class GroupedExperts(nn.Module):
     """E_local experts stored as batched weights; forward runs on tokens grouped (sorted) by local expert."""
 
-    def __init__(self, cfg: ModelConfig, num_local_experts: int, intermediate: int) -> None:
+    def __init__(self, cfg: ModelConfig, num_local_experts: int, intermediate: int, gated_act=None) -> None:
+        """`gated_act(h, valid_rows)`: a gated activation on the packed gate|up rows that replaces the config's
+        `hidden_act` (the experts are then gated whatever `cfg.glu` says)."""
         super().__init__()
         self.cfg, self.num_local_experts, self.intermediate = cfg, num_local_experts, intermediate
+        self.gated_act = gated_act
         H = cfg.hidden_size
-        up_out = 2 * intermediate if cfg.glu else intermediate
+        up_out = 2 * intermediate if (cfg.glu or gated_act is not None) else intermediate
         self.w_up = nn.Parameter(torch.empty(num_local_experts, up_out, H))      # gate|up fused
         self.w_down = nn.Parameter(torch.empty(num_local_experts, H, intermediate))
         nn.init.normal_(self.w_up, std=cfg.initializer_range)        # (on meta: recorded by the lazy-init log only)
@@ -79,6 +82,8 @@ class GroupedExperts(nn.Module):
         from ..moe.grouped_gemm import grouped_linear
 
         h = grouped_linear(x_sorted, self.w_up, counts)
+        if self.gated_act is not None:
+            return grouped_linear(self.gated_act(h, counts.sum()), self.w_down, counts)
         # rows past sum(counts) are padding of an over-allocated receive buffer: the activation skips them (the count
         # stays on the device)
         h = ops.glu(h, self.cfg.hidden_act, valid_rows=counts.sum()) if self.cfg.glu \
@@ -171,3 +176,56 @@ class SparseMoE(nn.Module):
         if hasattr(self, "shared_experts"):
             out = out + self.shared_experts(x2)
         return out.reshape(shape)
+
+
+class ClampedGLU(nn.Module):
+    """Gated feed-forward with a clamped activation: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit),
+    y = W_down (g * sigmoid(alpha * g) * (u + 1)); gate and up share one GEMM."""
+
+    def __init__(self, cfg: ModelConfig, intermediate: int, limit: float, alpha: float = 1.702) -> None:
+        super().__init__()
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.gate_up_proj = nn.Linear(cfg.hidden_size, 2 * intermediate, bias=False)
+        self.down_proj = nn.Linear(intermediate, cfg.hidden_size, bias=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down_proj(ops.clamped_glu(self.gate_up_proj(x), self.limit, self.alpha))
+
+
+class ClampedExpertFF(nn.Module):
+    """Routed feed-forward of a hybrid decoder layer (`LayerSpec.moe`): router scores = softmax over ALL experts in fp32,
+    the `top` largest are used with their scores renormalised to one (+ 1e-20 in the divisor); experts and the optional
+    shared expert are `ClampedGLU`s without biases.  The routed part runs as two grouped GEMMs over the token rows sorted
+    by expert and is combined in fp32 by a gather in a fixed order (row j of a token is its j-th choice), so a token's
+    result does not depend on what else is in the batch.  `forward` returns (routed sum fp32, shared output or None):
+    the caller adds both to the fp32 residual stream."""
+
+    def __init__(self, cfg: ModelConfig, spec) -> None:
+        super().__init__()
+        self.cfg, self.spec = cfg, spec
+        self.router = nn.Linear(cfg.hidden_size, spec.experts, bias=False)
+        self.experts = GroupedExperts(cfg, spec.experts, spec.ff, gated_act=self._act)
+        if spec.shared_ff:
+            self.shared = ClampedGLU(cfg, spec.shared_ff, spec.shared_limit, spec.alpha)
+        self.shard_config = None
+
+    def _act(self, h: torch.Tensor, valid_rows) -> torch.Tensor:
+        return ops.clamped_glu(h, self.spec.limit, self.spec.alpha, valid_rows=valid_rows if h.is_cuda else None)
+
+    def route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        from ..ops.moe import router_topk
+
+        logits = F.linear(x.float(), self.router.weight.float())
+        if x.dtype == torch.float32:            # 32-bit serving: IEEE exponentials
+            p = torch.softmax(logits, -1)
+            w, idx = torch.topk(p, self.spec.top, dim=-1)
+            return w / (w.sum(-1, keepdim=True) + 1e-20), idx
+        return router_topk(logits, self.spec.top, renormalize=True)
+
+    def forward(self, x: torch.Tensor) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        from ..moe import dispatch_combine
+
+        x2 = x.reshape(-1, x.shape[-1])
+        w, idx = self.route(x2)
+        routed = dispatch_combine.moe_forward_gather(x2, w, idx, self.experts, self.spec.experts)
+        return routed, (self.shared(x2) if self.spec.shared_ff else None)

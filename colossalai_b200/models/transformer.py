@@ -53,6 +53,9 @@ class SeqMeta:
     local_seqlen: Optional[int] = None          # per-sequence tokens held by this rank under a2a / ring_attn
     stream_cast: Optional[torch.Tensor] = None  # compute-dtype copy of an fp32 residual stream (written by the fused
                                                 # norm + residual kernel, read by the next sublayer's GEMM)
+    pending: Optional[list] = None              # fp32 stream: sublayer outputs not added yet (the next norm's kernel
+                                                # adds them) and a [W] vector added to every token (`pending_row`)
+    pending_row: Optional[torch.Tensor] = None
 
 
 def _use_fused_a2a(x: torch.Tensor, sp_group) -> bool:
@@ -72,7 +75,7 @@ def build_norm(cfg: ModelConfig, hidden: Optional[int] = None) -> nn.Module:
         norm = FusedRMSNorm(h, eps=cfg.norm_eps, offset=cfg.norm_weight_offset)
         norm.reset_parameters()
         return norm
-    return FusedLayerNorm(h, eps=cfg.norm_eps)
+    return FusedLayerNorm(h, eps=cfg.norm_eps, bias=cfg.norm_bias)
 
 
 def _sc(module: nn.Module):
@@ -321,7 +324,10 @@ class MLP(nn.Module):
             h = ops.glu(self.gate_up_proj(x), self.cfg.hidden_act)
         else:
             up = self.up_proj
-            if self.cfg.hidden_act in ("gelu", "gelu_new", "gelu_tanh", "gelu_pytorch_tanh") and x.is_cuda \
+            if x.is_cuda and x.dtype != torch.float32 and not torch.is_grad_enabled() and up.bias is None \
+                    and type(up) is nn.Linear and self.cfg.hidden_act in ("gelu_tanh", "gelu_new", "relu2"):
+                h = ops.bias_act(up(x), None, self.cfg.hidden_act)        # serving: one fused activation kernel
+            elif self.cfg.hidden_act in ("gelu", "gelu_new", "gelu_tanh", "gelu_pytorch_tanh") and x.is_cuda \
                     and getattr(up, "skip_bias_add", False):
                 y, b = up(x)
                 h = ops.bias_act(y, b, self.cfg.hidden_act)
@@ -342,10 +348,14 @@ class DecoderLayer(nn.Module):
             self.self_attn = build_mixer(cfg, layer_idx)
         else:
             self.self_attn = MLAttention(cfg, layer_idx) if cfg.use_mla else Attention(cfg, layer_idx)
-        if not cfg.parallel_block and (spec is None or spec.ff is not None):
+        if not cfg.parallel_block and (spec is None or spec.ff is not None or spec.moe is not None):
             self.post_attention_layernorm = build_norm(cfg)
         moe = cfg.moe
-        if spec is not None:
+        if spec is not None and spec.moe is not None:
+            from .moe import ClampedExpertFF
+
+            self.mlp = ClampedExpertFF(cfg, spec.moe)
+        elif spec is not None:
             self.mlp = MLP(cfg, spec.ff) if spec.ff is not None else None
         elif moe is not None and layer_idx >= moe.first_k_dense_replace and (layer_idx % moe.moe_layer_freq == 0):
             from .moe import SparseMoE
@@ -362,6 +372,8 @@ class DecoderLayer(nn.Module):
         if cfg.post_norm:   # BERT: x = LN(x + attn(x)); x = LN(x + mlp(x))
             x = self.input_layernorm(x + self.self_attn(x, meta, rope, kv_cache))
             return self.post_attention_layernorm(x + self.mlp(x))
+        if cfg.parallel_block and cfg.fp32_residual:
+            return self._forward_parallel_stream(x, meta, rope, kv_cache)
         if cfg.parallel_block:
             h = self.input_layernorm(x)
             return x + self.self_attn(h, meta, rope, kv_cache) + self.mlp(h)
@@ -374,6 +386,22 @@ class DecoderLayer(nn.Module):
             h = self.post_attention_layernorm(x)
         return x + self.mlp(h)
 
+
+    def _forward_parallel_stream(self, x: torch.Tensor, meta: SeqMeta, rope, kv_cache) -> torch.Tensor:
+        """Parallel block on an fp32 stream: h = norm(x); x <- x + (mixer(h) + ff(h)).  The sum is left PENDING
+        (`meta.pending`): the kernel that normalises the stream for the next layer (or the final norm) first adds the
+        pending outputs, in fp32, in one pass over x."""
+        cfg = self.cfg
+        norm = self.input_layernorm
+        h = ops.mixers.stream_add_norm(x, meta.pending or (), row=meta.pending_row, weight=norm.weight, eps=cfg.norm_eps,
+                                       kind=cfg.norm_type, offset=cfg.norm_weight_offset)
+        meta.pending_row = None
+        outs = [self.self_attn(h, meta, rope, kv_cache)]
+        if self.mlp is not None:
+            y = self.mlp(h)
+            outs += [t for t in (y if isinstance(y, tuple) else (y,)) if t is not None]
+        meta.pending = outs
+        return x
 
     def _forward_sublayer_out(self, x: torch.Tensor, meta: SeqMeta, rope, kv_cache) -> torch.Tensor:
         """x <- x + m * norm(mixer(x)); x <- x + m * norm(ff(x)): the sublayers read the stream itself and only their
@@ -415,6 +443,9 @@ class TransformerModel(nn.Module):
         self.layers = nn.ModuleList([DecoderLayer(cfg, i) for i in range(cfg.num_hidden_layers)])
         if cfg.final_norm:
             self.norm = build_norm(cfg)
+        if cfg.looped:
+            self.loop_step = nn.Parameter(torch.zeros(cfg.loop_times, cfg.hidden_size))
+        self.stream_trace: Optional[list] = None     # diagnostics: when a list, the fp32 stream after every layer run
         self.shard_config = None
         self.gradient_checkpointing = False
         self._rope_cache: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
@@ -569,12 +600,45 @@ class TransformerModel(nn.Module):
                                               else self.embed_tokens.weight.dtype)
         start, end = self.layer_range()
         n_ckpt = self._num_ckpt_layers(end - start) if self.training else 0
-        for i in range(start, end):
-            layer = self.layers[i]
-            if i - start < n_ckpt:
-                x = torch_checkpoint(layer, x, meta, rope, kv_cache, use_reentrant=False)
-            else:
-                x = layer(x, meta, rope, kv_cache)
+        stream = cfg.parallel_block and cfg.fp32_residual
+        if cfg.looped or stream:
+            # a span of layers may run several times with the same weights: every layer RUN has its own cache / state
+            # (the runtime is told which), and every pass starts by adding the embedding output (not the first) and the
+            # pass's learned vector to the stream
+            assert sm is None, "looped spans / pending-sum streams are not split over pipeline stages"
+            x0 = x
+            if cfg.looped:
+                x = x.clone()
+            for run, (i, t) in enumerate(cfg.layer_runs()):
+                if t is not None and i == cfg.loop_start:
+                    extra = ([x0] if t > 0 else [])
+                    if stream:
+                        meta.pending = (meta.pending or []) + extra
+                        meta.pending_row = self.loop_step[t]
+                    else:
+                        x = x + (x0 if t > 0 else 0) + self.loop_step[t].to(x.dtype)
+                if kv_cache is not None and hasattr(kv_cache, "bind_run"):
+                    kv_cache.bind_run(i, run)
+                x = self.layers[i](x, meta, rope, kv_cache)
+                if self.stream_trace is not None:
+                    if meta.pending:
+                        ops.mixers.stream_add_norm(x, meta.pending)
+                        meta.pending = None
+                    self.stream_trace.append(x.detach().float().clone())
+            if stream:
+                pend, meta.pending = meta.pending or (), None
+                if cfg.final_norm:
+                    return ops.mixers.stream_add_norm(x, pend, weight=self.norm.weight, eps=cfg.norm_eps,
+                                                      kind=cfg.norm_type, offset=cfg.norm_weight_offset)
+                ops.mixers.stream_add_norm(x, pend)
+                return x
+        else:
+            for i in range(start, end):
+                layer = self.layers[i]
+                if i - start < n_ckpt:
+                    x = torch_checkpoint(layer, x, meta, rope, kv_cache, use_reentrant=False)
+                else:
+                    x = layer(x, meta, rope, kv_cache)
         if last and cfg.final_norm:
             if cfg.fp32_residual and x.dtype == torch.float32:
                 x = ops.rms_norm_f32in(x, self.norm.weight, cfg.norm_eps, cfg.norm_weight_offset)
@@ -659,8 +723,12 @@ class TransformerLMHeadModel(nn.Module):
                 torch.func.functional_call(self.lm_head, {"weight": w}, (h,))
         else:
             logits = self.lm_head(h)
+        if cfg.logit_softcap:
+            logits = logits.float()
         if cfg.logit_scale != 1.0:
             logits = logits * cfg.logit_scale
+        if cfg.logit_softcap:                  # logits <- cap * tanh(logits / cap), in fp32
+            logits = cfg.logit_softcap * torch.tanh(logits / cfg.logit_softcap)
         out: Dict[str, torch.Tensor] = {}
         if labels is not None:
             class _NoShard:

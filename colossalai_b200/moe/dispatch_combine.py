@@ -61,6 +61,24 @@ def _padded_counts(counts: torch.Tensor) -> torch.Tensor:
     return pc
 
 
+def moe_forward_gather(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, experts,
+                       num_experts: int) -> torch.Tensor:
+    """Serving form without expert parallelism: x [T, H]; topk_w [T, k] fp32; topk_idx [T, k] -> fp32 [T, H].  Token rows
+    are sorted by expert (no padding: the forward grouped GEMM walks a device-side tile list), and the combine GATHERS
+    every token's k expert rows and sums them in fp32 in the order of its choices - no atomics, no host sync."""
+    from ..ops.moe import gather_combine
+
+    T, H = x.shape
+    k = topk_idx.shape[1]
+    flat_idx = topk_idx.reshape(-1)
+    order = torch.argsort(flat_idx, stable=True)
+    counts = torch.bincount(flat_idx, minlength=num_experts)
+    ys = experts(x.index_select(0, order // k), counts)                # [T*k, H] grouped by expert
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(T * k, device=x.device)
+    return gather_combine(ys, inv.view(T, k), topk_w)
+
+
 def moe_forward(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, experts, num_experts: int,
                 ep_group: Optional[dist.ProcessGroup]) -> torch.Tensor:
     """x [T, H]; topk_w [T, k] fp32; topk_idx [T, k] -> [T, H]."""

@@ -85,6 +85,31 @@ def glu(gate_up: torch.Tensor, act: str = "silu", valid_rows: Optional[torch.Ten
     return glu_ref(gate_up, act)
 
 
+def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float = 1.702,
+                valid_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Clamped gated unit on a packed [rows, 2 I] gate|up tensor: g = min(gate, limit), u = clamp(up, -limit, limit),
+    out = g * sigmoid(alpha * g) * (u + 1).  Forward only on the native path (IEEE fp32 arithmetic, one rounding);
+    `valid_rows` as in `glu`.  Tensors that need gradients take the PyTorch expression."""
+    I = gate_up.shape[-1] // 2
+    if use_native(gate_up) and not (torch.is_grad_enabled() and gate_up.requires_grad):
+        from .mixers import _get_lib as _mixers_lib
+
+        shape = gate_up.shape
+        gu = gate_up.contiguous().view(-1, 2 * I)
+        out = torch.empty(gu.shape[0], I, dtype=gu.dtype, device=gu.device)
+        if valid_rows is not None:
+            valid_rows = valid_rows.to(device=gu.device, dtype=torch.int64).reshape(1).contiguous()
+        loader.check(_mixers_lib().cb_clamped_glu(loader.ptr(gu), loader.ptr(out), ctypes.c_int64(gu.shape[0]), I,
+                                                  ctypes.c_float(limit), ctypes.c_float(alpha), code(gu.dtype),
+                                                  loader.ptr(valid_rows), loader.stream_ptr()), "clamped_glu")
+        loader.launch_counter.add("clamped_glu")
+        return out.view(shape[:-1] + (I,))
+    g, u = gate_up.float().chunk(2, dim=-1)
+    g = g.clamp(max=limit)
+    u = u.clamp(min=-limit, max=limit)
+    return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(gate_up.dtype)
+
+
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return glu(gate_up, "silu")
 

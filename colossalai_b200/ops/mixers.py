@@ -1,6 +1,8 @@
 """Python face of the sequence-mixer kernels (kernel/csrc/mixers.cu): short causal convolution with a carried window,
-recurrent state scans (decayed outer-product state, gated delta rule), group RMS norm with a sigmoid gate, RMS norm of a
-sublayer's output added to an fp32 residual stream, and paged attention with a distance-bucket bias and a softmax sink.
+recurrent state scans (decayed outer-product state with optional rotary positions, gated delta rule), group RMS norm
+with a sigmoid / silu gate, RMS norm of a sublayer's output added to an fp32 residual stream, sums into the fp32 stream
+fused with the next RMS / layer norm, rotary positions from an fp32 angle table, the cache rows of latent attention, and
+paged attention with a distance-bucket bias and a softmax sink (values optionally read from the key rows).
 
 All ops take a RAGGED step (`RaggedMeta`): for every live sequence its next tokens, how many tokens earlier steps
 consumed, and the slot that holds its carried state.  CUDA tensors go to the sm_100a kernels; CPU tensors take the plain
@@ -22,7 +24,7 @@ from ._dtypes import code
 
 __all__ = ["RaggedMeta", "short_conv_silu", "state_scan_decay", "state_scan_delta", "gated_group_rms_norm",
            "rms_norm_residual", "rms_norm_f32in", "paged_kv_write_mix", "paged_bias_attention", "log_bucket_starts",
-           "bucket_lut"]
+           "bucket_lut", "rotary_table", "rotary_half", "stream_add_norm", "latent_kv_write"]
 
 _lib = None
 _SPLIT_BELOW_TILES = 148        # attention steps with fewer CTAs than SMs split their keys
@@ -148,6 +150,56 @@ def bucket_lut(starts: Sequence[int]) -> torch.Tensor:
     return lut
 
 
+# ------------------------------------------------------------------------------------------------ rotary positions
+_rotary_tables = {}
+
+
+def rotary_table(min_len: int, dims: int, base: float, device) -> torch.Tensor:
+    """fp32 [positions, dims]: row p holds cos(p f_i) for i < dims / 2, then sin(p f_i), with f_i = base^(-2 i / dims).
+    Angles are formed in float64 and rounded once.  The table is cached per (dims, base, device) and grows in powers of
+    two, so that positions far beyond any configured length stay exact."""
+    key = (int(dims), float(base), str(device))
+    tab = _rotary_tables.get(key)
+    if tab is None or tab.shape[0] < min_len:
+        n = max(1024, 1 << max(int(min_len) - 1, 1).bit_length())
+        f = torch.tensor(float(base), dtype=torch.float64) ** (-torch.arange(0, dims, 2, dtype=torch.float64) / dims)
+        ang = torch.arange(n, dtype=torch.float64)[:, None] * f[None, :]
+        tab = torch.cat([ang.cos(), ang.sin()], 1).float().to(device)
+        _rotary_tables[key] = tab
+    return tab
+
+
+def _rot_ref(x: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, dims: int) -> torch.Tensor:
+    """x [T, H, w] fp32: channel i < dims / 2 of every head is paired with channel i + dims / 2."""
+    half = dims // 2
+    cs = table[pos.long()]
+    c, sn = cs[:, None, :half], cs[:, None, half:]
+    u, v = x[..., :half], x[..., half:dims]
+    return torch.cat([u * c - v * sn, v * c + u * sn, x[..., dims:]], -1)
+
+
+def rotary_half(src: torch.Tensor, dst: torch.Tensor, heads: int, src_head_stride: int, src_off: int,
+                dst_head_stride: int, dst_off: int, width: int, dims: int, table: torch.Tensor,
+                token_pos: torch.Tensor) -> None:
+    """For every token t and head h: dst[t, h * dst_head_stride + dst_off + (0..width)] = the `width` channels at
+    src[t, h * src_head_stride + src_off + ..] with the first `dims` of them turned by the token's position (rotate-half
+    pairs, fp32 arithmetic, one rounding into dst's dtype)."""
+    T = src.shape[0]
+    if use_native(src):
+        assert src.stride(1) == 1 and dst.stride(1) == 1 and table.dtype == torch.float32 and table.shape[1] == dims
+        loader.check(_get_lib().cb_rotary_half(
+            loader.ptr(src), _i64(src.stride(0)), loader.ptr(dst), _i64(dst.stride(0)), _i64(T), heads, src_head_stride,
+            src_off, dst_head_stride, dst_off, width, dims, loader.ptr(table), loader.ptr(token_pos), code(src.dtype),
+            code(dst.dtype), loader.stream_ptr()), "rotary_half")
+        loader.launch_counter.add("rotary_half")
+        return
+    cols = (torch.arange(heads)[:, None] * src_head_stride + src_off + torch.arange(width)[None, :]).reshape(-1)
+    x = src[:, cols].float().view(T, heads, width)
+    y = _rot_ref(x, token_pos, table, dims)
+    dcols = (torch.arange(heads)[:, None] * dst_head_stride + dst_off + torch.arange(width)[None, :]).reshape(-1)
+    dst[:, dcols] = y.reshape(T, heads * width).to(dst.dtype)
+
+
 # ------------------------------------------------------------------------------------------------ short convolution
 def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, meta: RaggedMeta,
                     activation: bool = True) -> torch.Tensor:
@@ -183,7 +235,7 @@ def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, 
 
 # ------------------------------------------------------------------------------------------------ state scans
 def _scan_native(mode, q, k, v, araw, braw, head_decay, a_log, dt_bias, state, meta, heads, qk_heads, dim, vdim,
-                 act_silu, unit_qk, unit_eps, q_scale):
+                 act_silu, unit_qk, unit_eps, q_scale, k_scale=1.0, rot_table=None, rot_dims=0):
     T = q.shape[0]
     out = torch.empty(T, heads * vdim, dtype=torch.float32, device=q.device)
     for t in (q, k, v):
@@ -198,20 +250,26 @@ def _scan_native(mode, q, k, v, araw, braw, head_decay, a_log, dt_bias, state, m
         loader.ptr(braw), ld(braw), loader.ptr(head_decay), loader.ptr(a_log), loader.ptr(dt_bias), loader.ptr(state),
         loader.ptr(out), loader.ptr(work), _i64(T), loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len),
         loader.ptr(meta.slots), meta.nseq, heads, qk_heads, dim, vdim, int(act_silu), int(unit_qk), _f(unit_eps),
-        _f(q_scale), code(q.dtype), loader.stream_ptr()), "state_scan")
+        _f(q_scale), _f(k_scale), loader.ptr(rot_table), int(rot_dims if rot_table is not None else 0),
+        loader.ptr(meta.token_pos), code(q.dtype), loader.stream_ptr()), "state_scan")
     loader.launch_counter.add("state_scan", 2)
     return out
 
 
 def state_scan_decay(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, head_decay: torch.Tensor, state: torch.Tensor,
-                     meta: RaggedMeta, heads: int, dim: int, vdim: int, act_silu: bool = True) -> torch.Tensor:
+                     meta: RaggedMeta, heads: int, dim: int, vdim: int, act_silu: bool = True,
+                     rot_table: Optional[torch.Tensor] = None, rot_dims: int = 0, q_scale: float = 1.0,
+                     k_scale: float = 1.0) -> torch.Tensor:
     """Decayed outer-product memory per head: every token scales the head's matrix M [dim, vdim] by the head's decay,
-    adds outer(k, v) and reads y = M^T q (q, k, v through silu first when `act_silu`).  q, k [T, heads x dim], v [T, heads x vdim]; state [slots, heads, dim, vdim] fp32.  Returns fp32 o."""
+    adds outer(k, v) and reads y = M^T q (q, k, v through silu first when `act_silu`).  With `rot_table`
+    (`rotary_table`) the first `rot_dims` channels of every q / k head are turned by the token's position, in fp32, before
+    `q_scale` / `k_scale` multiply them.  q, k [T, heads x dim], v [T, heads x vdim]; state [slots, heads, dim, vdim] fp32.
+    Returns fp32 o."""
     if dim > 128:
         raise NotImplementedError("state_scan: key width above 128 is not supported")
     if use_native(q):
         return _scan_native(0, q, k, v, None, None, head_decay, None, None, state, meta, heads, heads, dim, vdim,
-                            act_silu, False, 0.0, 1.0)
+                            act_silu, False, 0.0, q_scale, k_scale, rot_table, rot_dims)
     T = q.shape[0]
     out = torch.empty(T, heads * vdim, dtype=torch.float32)
     act = F.silu if act_silu else (lambda z: z)
@@ -224,6 +282,10 @@ def state_scan_decay(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, head_dec
         qq = act(q[t0:t0 + n].float()).view(n, heads, dim)
         kk = act(k[t0:t0 + n].float()).view(n, heads, dim)
         vv = act(v[t0:t0 + n].float()).view(n, heads, vdim)
+        if rot_table is not None and rot_dims > 0:
+            qq = _rot_ref(qq, meta.token_pos[t0:t0 + n], rot_table, rot_dims)
+            kk = _rot_ref(kk, meta.token_pos[t0:t0 + n], rot_table, rot_dims)
+        qq, kk = qq * q_scale, kk * k_scale
         for t in range(n):
             S = dec * S + kk[t][:, :, None] * vv[t][:, None, :]
             out[t0 + t] = torch.einsum("hdv,hd->hv", S, qq[t]).reshape(-1)
@@ -276,24 +338,29 @@ def state_scan_delta(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_pr
 
 
 # ------------------------------------------------------------------------------------------------ norms
-def gated_group_rms_norm(o: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], group: int, eps: float,
-                         out_dtype: torch.dtype) -> torch.Tensor:
+def gated_group_rms_norm(o: torch.Tensor, weight: Optional[torch.Tensor], gate: Optional[torch.Tensor], group: int,
+                         eps: float, out_dtype: torch.dtype, gate_act: str = "sigmoid") -> torch.Tensor:
     """o [T, C] fp32 -> o / sqrt(mean over each group of `group` channels + eps) * weight[c % len(weight)]
-    * sigmoid(gate), in `out_dtype`."""
+    * act(gate), in `out_dtype`; act is the sigmoid or (`gate_act="silu"`) the silu; without `weight` the norm is plain."""
     T, C = o.shape
+    assert gate_act in ("sigmoid", "silu")
     if use_native(o):
         out = torch.empty(T, C, dtype=out_dtype, device=o.device)
-        assert o.is_contiguous() and weight.dtype == out_dtype and (gate is None or gate.stride(1) == 1)
+        assert o.is_contiguous() and (weight is None or weight.dtype == out_dtype) and \
+            (gate is None or (gate.stride(1) == 1 and gate.dtype == out_dtype))
         loader.check(_get_lib().cb_gated_group_rmsnorm(
-            loader.ptr(o), loader.ptr(weight), weight.numel(), loader.ptr(gate), _i64(0 if gate is None else gate.stride(0)),
-            loader.ptr(out), _i64(T), C, group, _f(eps), code(out_dtype), loader.stream_ptr()), "gated_group_rmsnorm")
+            loader.ptr(o), loader.ptr(weight), 1 if weight is None else weight.numel(), loader.ptr(gate),
+            _i64(0 if gate is None else gate.stride(0)), loader.ptr(out), _i64(T), C, group, _f(eps),
+            int(gate_act == "silu"), code(out_dtype), loader.stream_ptr()), "gated_group_rmsnorm")
         loader.launch_counter.add("gated_group_rmsnorm")
         return out
     y = o.view(T, C // group, group)
     y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)
-    y = y.reshape(T, C) * weight.float().repeat(C // weight.numel())
+    y = y.reshape(T, C)
+    if weight is not None:
+        y = y * weight.float().repeat(C // weight.numel())
     if gate is not None:
-        y = y * torch.sigmoid(gate.float())
+        y = y * (torch.sigmoid(gate.float()) if gate_act == "sigmoid" else F.silu(gate.float()))
     return y.to(out_dtype)
 
 
@@ -329,7 +396,84 @@ def rms_norm_f32in(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: fl
     return (xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps) * (offset + weight.float())).to(weight.dtype)
 
 
+_NORM_KINDS = {None: 0, "none": 0, "rms": 1, "layer": 2}
+
+
+def stream_add_norm(x: torch.Tensor, addends: Sequence[torch.Tensor] = (), row: Optional[torch.Tensor] = None,
+                    weight: Optional[torch.Tensor] = None, eps: float = 1e-5, kind: Optional[str] = None,
+                    offset: float = 0.0, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """The fp32 residual stream x [T, W], updated in place: x += sum(addends) (+ `row` [W] for every token), the addends
+    summed among themselves first, all in fp32.  Addends are [T, W] in the compute dtype or fp32 (at most four).  With
+    `kind` "rms" / "layer" the new x is normalised in the same pass - x / sqrt(mean x^2 + eps) or
+    (x - mean) / sqrt(mean of squared deviations + eps), times (offset + weight) - and returned in `out_dtype` (default: the
+    weight's dtype).  One kernel sums a layer's sublayer outputs into the stream and feeds the next layer's GEMMs."""
+    T, W = x.shape
+    assert x.dtype == torch.float32 and len(addends) <= 4
+    k = _NORM_KINDS[kind]
+    if k and out_dtype is None:
+        out_dtype = weight.dtype
+    if use_native(x):
+        assert x.is_contiguous() and all(a.stride(1) == 1 and a.shape == x.shape for a in addends)
+        h = torch.empty(T, W, dtype=out_dtype, device=x.device) if k else None
+        if row is not None:
+            row = row.float().contiguous()
+        ad = list(addends) + [None] * (4 - len(addends))
+        if weight is not None and k:
+            assert weight.dtype in (out_dtype, torch.float32)
+        loader.check(_get_lib().cb_stream_add_norm(
+            loader.ptr(x), loader.ptr(ad[0]), _i64(0 if ad[0] is None else ad[0].stride(0)),
+            code(ad[0].dtype) if ad[0] is not None else 0, loader.ptr(ad[1]), _i64(0 if ad[1] is None else ad[1].stride(0)),
+            code(ad[1].dtype) if ad[1] is not None else 0, loader.ptr(ad[2]), _i64(0 if ad[2] is None else ad[2].stride(0)),
+            code(ad[2].dtype) if ad[2] is not None else 0, loader.ptr(ad[3]), _i64(0 if ad[3] is None else ad[3].stride(0)),
+            code(ad[3].dtype) if ad[3] is not None else 0, loader.ptr(row),
+            loader.ptr(weight if k else None), code(weight.dtype) if (k and weight is not None) else 0, loader.ptr(h),
+            code(out_dtype) if k else 0, _i64(T), W, k, _f(eps), _f(offset), loader.stream_ptr()), "stream_add_norm")
+        loader.launch_counter.add("stream_add_norm")
+        return h
+    if len(addends) or row is not None:
+        acc = None
+        for a in addends:
+            acc = a.float() if acc is None else acc + a.float()
+        if row is not None:
+            acc = row.float()[None, :] if acc is None else acc + row.float()[None, :]
+        x += acc
+    if not k:
+        return None
+    if k == 1:
+        y = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+    else:
+        d = x - x.mean(-1, keepdim=True)
+        y = d / torch.sqrt((d * d).mean(-1, keepdim=True) + eps)
+    return (y * (offset + weight.float())).to(out_dtype)
+
+
 # ------------------------------------------------------------------------------------------------ paged attention
+def latent_kv_write(z: torch.Tensor, norm_weight: torch.Tensor, eps: float, kv_rank: int, rot_table: torch.Tensor,
+                    cache: torch.Tensor, block_tables: torch.Tensor, meta: RaggedMeta) -> None:
+    """The cache rows of latent attention.  z [T, kv_rank + rot]: the first `kv_rank` columns are RMS-normalised with
+    `norm_weight` (the latent), the others are turned by the token's position (the rotated key part all heads share);
+    both go, rounded once, into the token's row of the paged cache [blocks, block_size, 1, kv_rank + rot]."""
+    T, Wz = z.shape
+    rot = Wz - kv_rank
+    bs = cache.shape[1]
+    if use_native(z):
+        assert z.stride(1) == 1 and cache.is_contiguous() and cache.shape[-1] == Wz and rot_table.shape[1] == rot
+        loader.check(_get_lib().cb_latent_kv_write(
+            loader.ptr(z), _i64(z.stride(0)), loader.ptr(norm_weight), code(norm_weight.dtype), _f(eps), kv_rank, rot,
+            loader.ptr(rot_table), loader.ptr(cache), loader.ptr(block_tables), loader.ptr(meta.token_seq),
+            loader.ptr(meta.token_pos), _i64(T), bs, block_tables.shape[1], code(z.dtype), loader.stream_ptr()),
+            "latent_kv_write")
+        loader.launch_counter.add("latent_kv_write")
+        return
+    zf = z.float()
+    c = zf[:, :kv_rank]
+    c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * norm_weight.float()
+    kr = _rot_ref(zf[:, None, kv_rank:], meta.token_pos, rot_table, rot)[:, 0]
+    blk = block_tables[meta.token_seq.long(), (meta.token_pos // bs).long()].long()
+    off = (meta.token_pos % bs).long()
+    cache.view(cache.shape[0], bs, Wz)[blk, off] = torch.cat([c, kr], -1).to(cache.dtype)
+
+
 def paged_kv_write_mix(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                        block_tables: torch.Tensor, meta: RaggedMeta, v_other: Optional[torch.Tensor] = None,
                        lam: float = 0.0) -> None:
@@ -358,8 +502,11 @@ def paged_kv_write_mix(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, 
 def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
                          meta: RaggedMeta, scale: float, bias_table: Optional[torch.Tensor] = None,
                          bucket_starts: Optional[torch.Tensor] = None, sink: bool = False,
-                         lut: Optional[torch.Tensor] = None, tensor_cores: Optional[bool] = None) -> torch.Tensor:
+                         lut: Optional[torch.Tensor] = None, tensor_cores: Optional[bool] = None,
+                         vdim: Optional[int] = None) -> torch.Tensor:
     """Causal attention of every step token over positions 0..pos of its sequence in the paged cache.
+    With `vdim` given and `v_cache` the key cache itself, the values are the first `vdim` columns of the key rows (latent
+    attention: one row per token serves as key and value).
     q [T, heads x dim]; caches [blocks, block_size, kv_heads, dim | vdim]; bias_table [buckets, heads] fp32 indexed by
     the bucket of the distance (`bucket_starts` [buckets] int32: smallest distance of each bucket); `sink` adds a key of
     score 0 without a value to the softmax.  Returns [T, heads x vdim].
@@ -369,16 +516,17 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     `tensor_cores` forces the choice."""
     T = q.shape[0]
     _, bs, G, dim = k_cache.shape
-    vdim = v_cache.shape[3]
+    ldv = v_cache.shape[3]                     # elements between the value rows of consecutive (token, kv head) pairs
+    vdim = ldv if vdim is None else vdim
     heads = q.shape[1] // dim
     nb = 0 if bias_table is None else bias_table.shape[0]
     if use_native(q):
-        if vdim > 256:
-            raise NotImplementedError("paged_bias_attention: value width above 256 is not supported")
+        if vdim > 512:
+            raise NotImplementedError("paged_bias_attention: value width above 512 is not supported")
         assert q.stride(1) == 1 and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
         out = torch.empty(T, heads * vdim, dtype=q.dtype, device=q.device)
         mma_ok = (q.dtype in (torch.bfloat16, torch.float16) and dim % 8 == 0 and vdim % 8 == 0 and dim <= 128
-                  and vdim <= 128 and nb <= 255 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+                  and vdim <= 128 and nb <= 255 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and ldv % 8 == 0)
         if tensor_cores is None:
             tensor_cores = mma_ok
         if tensor_cores:
@@ -405,7 +553,7 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                 loader.ptr(q), _i64(q.stride(0)), loader.ptr(k_cache), loader.ptr(v_cache), loader.ptr(block_tables),
                 loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len), loader.ptr(meta.token_pos), loader.ptr(bias_table),
                 loader.ptr(lut), 0 if lut is None else lut.numel(), nb, loader.ptr(out), _i64(T), meta.nseq, meta.max_q,
-                heads, G, dim, vdim, bs, block_tables.shape[1], _f(scale), int(sink), chunk, splits,
+                heads, G, dim, vdim, ldv, bs, block_tables.shape[1], _f(scale), int(sink), chunk, splits,
                 loader.ptr(part_o), loader.ptr(part_ml), code(q.dtype), loader.stream_ptr()),
                 "paged_bias_attention_mma")
             loader.launch_counter.add("paged_bias_attention_mma")
@@ -413,7 +561,7 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         loader.check(_get_lib().cb_paged_bias_attention(
             loader.ptr(q), _i64(q.stride(0)), loader.ptr(k_cache), loader.ptr(v_cache), loader.ptr(block_tables),
             loader.ptr(meta.token_seq), loader.ptr(meta.token_pos), loader.ptr(bias_table), loader.ptr(bucket_starts), nb,
-            loader.ptr(out), _i64(T), heads, G, dim, vdim, bs, block_tables.shape[1], _f(scale), int(sink),
+            loader.ptr(out), _i64(T), heads, G, dim, vdim, ldv, bs, block_tables.shape[1], _f(scale), int(sink),
             code(q.dtype), loader.stream_ptr()), "paged_bias_attention")
         loader.launch_counter.add("paged_bias_attention")
         return out
@@ -426,7 +574,7 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         L = c + n
         blks = block_tables[i, :(L + bs - 1) // bs].long()
         kk = k_cache[blks].reshape(-1, G, dim)[:L].float().repeat_interleave(rep, 1)
-        vv = v_cache[blks].reshape(-1, G, vdim)[:L].float().repeat_interleave(rep, 1)
+        vv = v_cache[blks].reshape(-1, G, ldv)[:L, :, :vdim].float().repeat_interleave(rep, 1)
         qq = q[t0:t0 + n].float().view(n, heads, dim)
         s = torch.einsum("ihd,jhd->hij", qq, kk) * scale
         dist = torch.arange(c, L)[:, None] - torch.arange(L)[None, :]

@@ -150,3 +150,21 @@ def router_topk(logits: torch.Tensor, k: int, renormalize: bool = True, return_p
     if renormalize:
         w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
     return (w, idx, probs) if return_probs else (w, idx)
+
+
+def gather_combine(rows: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_j weights[t, j] * rows[row_of[t, j]] in fp32, j ascending.  rows [N, H] (any float dtype), row_of
+    [T, k] int64, weights [T, k] fp32 -> fp32 [T, H]."""
+    T, k = row_of.shape
+    H = rows.shape[1]
+    if use_native(rows):
+        out = torch.empty(T, H, dtype=torch.float32, device=rows.device)
+        loader.check(_get_lib().cb_moe_gather_combine(loader.ptr(rows.contiguous()), loader.ptr(row_of.contiguous()),
+                                                      loader.ptr(weights.float().contiguous()), loader.ptr(out), T, k, H,
+                                                      code(rows.dtype), loader.stream_ptr()), "moe_gather_combine")
+        loader.launch_counter.add("moe_gather_combine")
+        return out
+    out = torch.zeros(T, H, dtype=torch.float32, device=rows.device)
+    for j in range(k):
+        out = out + weights[:, j:j + 1].float() * rows.index_select(0, row_of[:, j]).float()
+    return out
