@@ -386,6 +386,11 @@ class LLMEngine(BaseEngine):
         those of the longest context the page table can hold, kernels leave early where a sequence is shorter."""
         from ...models.transformer import SeqMeta
 
+        specs = getattr(self.model_config, "layer_specs", None) or []
+        if self.dtype == torch.float32 and any(getattr(sp, "moe", None) is not None for sp in specs):
+            # 32-bit routed experts run one exact GEMM per expert with host-side row counts: not capturable
+            self.logger.warning("CUDA graphs disabled: routed feed-forwards in float32 are not capturable", ranks=[0])
+            return
         rt = self.kv_runtime
         max_blocks = self.request_handler.cache_manager.get_max_blocks_per_sequence()
         max_ctx = max_blocks * self.inference_config.block_size - 1

@@ -544,40 +544,99 @@ struct StreamArgs {
   float eps, offset;
 };
 
-CB_DEVICE float load_any(const void* p, int dtype, int64_t i) {
-  if (dtype == CB_F32) return ((const float*)p)[i];
-  if (dtype == CB_BF16) return __bfloat162float(((const __nv_bfloat16*)p)[i]);
-  return __half2float(((const __half*)p)[i]);
+// VEC consecutive values of a row in any float dtype (VEC = 4: one 16-byte or 8-byte access)
+template <int VEC> CB_DEVICE void load_any(const void* p, int dtype, int64_t i, float (&v)[VEC]) {
+  if (dtype == CB_F32) {
+    struct alignas(4 * VEC) P { float e[VEC]; };
+    const P a = *reinterpret_cast<const P*>((const float*)p + i);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) v[e] = a.e[e];
+  } else if (dtype == CB_BF16) {
+    struct alignas(2 * VEC) P { __nv_bfloat16 e[VEC]; };
+    const P a = *reinterpret_cast<const P*>((const __nv_bfloat16*)p + i);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) v[e] = __bfloat162float(a.e[e]);
+  } else {
+    struct alignas(2 * VEC) P { __half e[VEC]; };
+    const P a = *reinterpret_cast<const P*>((const __half*)p + i);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) v[e] = __half2float(a.e[e]);
+  }
 }
-CB_DEVICE void store_any(void* p, int dtype, int64_t i, float v) {
-  if (dtype == CB_F32) ((float*)p)[i] = v;
-  else if (dtype == CB_BF16) ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
-  else ((__half*)p)[i] = __float2half_rn(v);
+template <int VEC> CB_DEVICE void store_any(void* p, int dtype, int64_t i, const float (&v)[VEC]) {
+  if (dtype == CB_F32) {
+    struct alignas(4 * VEC) P { float e[VEC]; };
+    P a;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) a.e[e] = v[e];
+    *reinterpret_cast<P*>((float*)p + i) = a;
+  } else if (dtype == CB_BF16) {
+    struct alignas(2 * VEC) P { __nv_bfloat16 e[VEC]; };
+    P a;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) a.e[e] = __float2bfloat16_rn(v[e]);
+    *reinterpret_cast<P*>((__nv_bfloat16*)p + i) = a;
+  } else {
+    struct alignas(2 * VEC) P { __half e[VEC]; };
+    P a;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) a.e[e] = __float2half_rn(v[e]);
+    *reinterpret_cast<P*>((__half*)p + i) = a;
+  }
 }
 
+// new stream values of VEC columns starting at i: x + (sum of the addends + row), written back when anything was added
+template <int VEC> CB_DEVICE void stream_take(const StreamArgs& g, float* xr, int64_t t, int i, float (&xv)[VEC]) {
+  float add[VEC];
+  bool any = false;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (g.a[j].p != nullptr) {
+      float v[VEC];
+      load_any<VEC>(g.a[j].p, g.a[j].dtype, t * g.a[j].ld + i, v);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) add[e] = any ? add[e] + v[e] : v[e];
+      any = true;
+    }
+  if (g.row != nullptr) {
+    float v[VEC];
+    load_any<VEC>(g.row, CB_F32, i, v);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) add[e] = any ? add[e] + v[e] : v[e];
+    any = true;
+  }
+  load_any<VEC>(xr, CB_F32, i, xv);
+  if (any) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) xv[e] += add[e];
+    store_any<VEC>(xr, CB_F32, i, xv);
+  }
+}
+
+template <int VEC>
 __global__ void __launch_bounds__(STREAM_THREADS) stream_add_norm_kernel(StreamArgs g) {
+  constexpr int STEP = STREAM_THREADS * VEC;
   __shared__ float red[64];
   const int64_t t = blockIdx.x;
   const int W = g.W;
   float* xr = g.x + t * W;
-  float keep[STREAM_ITEMS];
+  float keep[STREAM_ITEMS][VEC];
   float sum[1] = {0.f};
-  int n = 0;
-  for (int i = threadIdx.x; i < W; i += STREAM_THREADS, ++n) {
-    float add = 0.f;
-    bool any = false;
+  const int i0 = threadIdx.x * VEC;
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (g.a[j].p != nullptr) {
-        const float v = load_any(g.a[j].p, g.a[j].dtype, t * g.a[j].ld + i);
-        add = any ? add + v : v;
-        any = true;
-      }
-    if (g.row != nullptr) { add = any ? add + g.row[i] : g.row[i]; any = true; }
-    float xv = xr[i];
-    if (any) { xv += add; xr[i] = xv; }
-    if (n < STREAM_ITEMS) keep[n] = xv;
-    sum[0] += g.norm == 1 ? xv * xv : xv;
+  for (int n = 0; n < STREAM_ITEMS; ++n) {
+    const int i = i0 + n * STEP;
+    if (i < W) {
+      stream_take<VEC>(g, xr, t, i, keep[n]);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) sum[0] += g.norm == 1 ? keep[n][e] * keep[n][e] : keep[n][e];
+    }
+  }
+  for (int i = i0 + STREAM_ITEMS * STEP; i < W; i += STEP) {       // rows wider than the registers hold
+    float xv[VEC];
+    stream_take<VEC>(g, xr, t, i, xv);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) sum[0] += g.norm == 1 ? xv[e] * xv[e] : xv[e];
   }
   if (g.norm == 0) return;
   block_sum<1>(sum, red);
@@ -587,19 +646,35 @@ __global__ void __launch_bounds__(STREAM_THREADS) stream_add_norm_kernel(StreamA
   } else {
     mean = sum[0] / (float)W;
     float sq[1] = {0.f};
-    n = 0;
-    for (int i = threadIdx.x; i < W; i += STREAM_THREADS, ++n) {
-      const float d = (n < STREAM_ITEMS ? keep[n] : xr[i]) - mean;
-      sq[0] = fmaf(d, d, sq[0]);
+#pragma unroll
+    for (int n = 0; n < STREAM_ITEMS; ++n)
+      if (i0 + n * STEP < W) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { const float d = keep[n][e] - mean; sq[0] = fmaf(d, d, sq[0]); }
+      }
+    for (int i = i0 + STREAM_ITEMS * STEP; i < W; i += STEP) {
+      float xv[VEC];
+      load_any<VEC>(xr, CB_F32, i, xv);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) { const float d = xv[e] - mean; sq[0] = fmaf(d, d, sq[0]); }
     }
     block_sum<1>(sq, red);
     r = 1.f / sqrtf(sq[0] / (float)W + g.eps);
   }
-  n = 0;
-  for (int i = threadIdx.x; i < W; i += STREAM_THREADS, ++n) {
-    const float xv = n < STREAM_ITEMS ? keep[n] : xr[i];
-    const float wv = g.offset + (g.w != nullptr ? load_any(g.w, g.w_dtype, i) : 1.f);
-    store_any(g.h, g.h_dtype, t * W + i, (xv - mean) * r * wv);
+  auto emit = [&](int i, const float (&xv)[VEC]) {
+    float wv[VEC], y[VEC];
+    if (g.w != nullptr) load_any<VEC>(g.w, g.w_dtype, i, wv);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) y[e] = (xv[e] - mean) * r * (g.offset + (g.w != nullptr ? wv[e] : 1.f));
+    store_any<VEC>(g.h, g.h_dtype, t * W + i, y);
+  };
+#pragma unroll
+  for (int n = 0; n < STREAM_ITEMS; ++n)
+    if (i0 + n * STEP < W) emit(i0 + n * STEP, keep[n]);
+  for (int i = i0 + STREAM_ITEMS * STEP; i < W; i += STEP) {
+    float xv[VEC];
+    load_any<VEC>(xr, CB_F32, i, xv);
+    emit(i, xv);
   }
 }
 
@@ -665,17 +740,26 @@ __global__ void __launch_bounds__(128) latent_kv_write_kernel(const T* __restric
 
 // ------------------------------------------------------------------------------------------------ clamped gated unit
 // gu [rows, 2 I] = gate | up.  IEEE fp32 arithmetic (this file is built without fast math), one rounding into T.
-template <typename T>
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t rows, int I,
                                                           float limit, float alpha, const int64_t* __restrict__ row_limit) {
+  struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
   if (row_limit != nullptr) rows = min(rows, *row_limit);
-  const int64_t total = rows * I;
+  const int per_row = I / VEC;
+  const int64_t total = rows * per_row;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = idx / I;
-    const int c = (int)(idx - r * I);
-    const float gq = fminf(to_f32<T>(gu[r * 2 * I + c]), limit);
-    const float u = fminf(fmaxf(to_f32<T>(gu[r * 2 * I + I + c]), -limit), limit);
-    out[idx] = from_f32<T>(gq * sigmoid_f(alpha * gq) * (u + 1.f));
+    const int64_t r = idx / per_row;
+    const int c = (int)(idx - r * per_row) * VEC;
+    const Pack gp = *reinterpret_cast<const Pack*>(gu + r * 2 * I + c);
+    const Pack up = *reinterpret_cast<const Pack*>(gu + r * 2 * I + I + c);
+    Pack o;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const float gq = fminf(to_f32<T>(gp.v[e]), limit);
+      const float u = fminf(fmaxf(to_f32<T>(up.v[e]), -limit), limit);
+      o.v[e] = from_f32<T>(gq * sigmoid_f(alpha * gq) * (u + 1.f));
+    }
+    *reinterpret_cast<Pack*>(out + r * I + c) = o;
   }
 }
 
@@ -837,7 +921,7 @@ CB_DEVICE void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
 }
 
 template <typename T, int D, int MT>
-__global__ void __launch_bounds__(128, MT == 2 ? 2 : 3) paged_bias_attention_mma_kernel(
+__global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bias_attention_mma_kernel(
     const T* __restrict__ q, int64_t ldq, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const float* __restrict__ bias_table, const uint8_t* __restrict__ lut, int lut_n, int nbuckets, T* __restrict__ out,
@@ -849,8 +933,11 @@ __global__ void __launch_bounds__(128, MT == 2 ? 2 : 3) paged_bias_attention_mma
   constexpr int NR = 2 * MT;                    // rows a thread owns: (m-tile, upper / lower half)
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  T* KV = reinterpret_cast<T*>(smem_raw);       // [2 stages][K tile | V tile]
-  T* Qs = KV + 4 * TILE;                        // [BM][LDS]
+  // values that live in the key rows (latent attention: value = the row's first vdim columns): the K tile serves as V
+  const bool kv_same = v_cache == k_cache && ldv == dim;
+  const int stage_elems = kv_same ? TILE : 2 * TILE;
+  T* KV = reinterpret_cast<T*>(smem_raw);       // [2 stages][K tile | V tile] (no V tile when the K tile serves as V)
+  T* Qs = KV + 2 * stage_elems;                 // [BM][LDS]
   float* tab = reinterpret_cast<float*>(Qs + BM * LDS);              // [nbuckets][R] of this kv head's group
   const int s = blockIdx.z, g = blockIdx.y;
   const int R = heads / kv_heads;
@@ -866,12 +953,10 @@ __global__ void __launch_bounds__(128, MT == 2 ? 2 : 3) paged_bias_attention_mma
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
   for (int i = tid; i < nbuckets * R; i += 128) tab[i] = bias_table[(i / R) * heads + g * R + (i % R)] * LOG2E;
   const int* bt = block_tables + (int64_t)s * max_blocks;
-  // values that live in the key rows (latent attention: value = the row's first vdim columns): the K tile serves as V
-  const bool kv_same = v_cache == k_cache && ldv == dim;
 
   auto load_tile = [&](int stage, int j0) {
     constexpr int CH = D / 8;
-    T* Ks = KV + stage * 2 * TILE;
+    T* Ks = KV + stage * stage_elems;
     T* Vs = Ks + TILE;
     for (int idx = tid; idx < MMA_BN * CH; idx += 128) {
       const int r = idx / CH, c8 = (idx % CH) * 8;
@@ -936,7 +1021,7 @@ __global__ void __launch_bounds__(128, MT == 2 ? 2 : 3) paged_bias_attention_mma
     }
     __syncthreads();
     if (j0 <= whi) {                            // warp-uniform: otherwise the whole tile is masked for this warp
-      const T* Ks = KV + stage * 2 * TILE;
+      const T* Ks = KV + stage * stage_elems;
       const T* Vs = kv_same ? Ks : Ks + TILE;
       float sacc[MT][MMA_BN / 8][4];
 #pragma unroll
@@ -1133,7 +1218,8 @@ int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const 
                          int sink, int chunk, int max_splits, float* part_o, float* part_ml, cudaStream_t st) {
   const int R = heads / kv_heads;
   constexpr int BM = 64 * MT;
-  const size_t smem = (size_t)(4 * MMA_BN + BM) * (D + 8) * sizeof(T) + (size_t)nbuckets * R * sizeof(float);
+  const bool kv_same = v_cache == k_cache && ldv == dim;
+  const size_t smem = (size_t)((kv_same ? 2 : 4) * MMA_BN + BM) * (D + 8) * sizeof(T) + (size_t)nbuckets * R * sizeof(float);
   auto kern = paged_bias_attention_mma_kernel<T, D, MT>;
   static bool configured = false;               // per instantiation: opt in to large shared memory, all of it for CTAs
   if (!configured) {
@@ -1255,7 +1341,12 @@ int cb_stream_add_norm(float* x, const void* a0, int64_t ld0, int dt0, const voi
   if (norm < 0 || norm > 2 || (norm != 0 && h == nullptr)) return (int)cudaErrorInvalidValue;
   StreamArgs g{x, {{a0, ld0, dt0}, {a1, ld1, dt1}, {a2, ld2, dt2}, {a3, ld3, dt3}}, row, w, w_dtype, h, h_dtype, W, norm,
                eps, offset};
-  stream_add_norm_kernel<<<(unsigned)tokens, STREAM_THREADS, 0, st>>>(g);
+  // four columns per access when every row start and width allows it
+  bool vec = W % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)row & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
+             ((uintptr_t)h & 15) == 0;
+  for (int j = 0; j < 4; ++j) vec = vec && (g.a[j].p == nullptr || (g.a[j].ld % 4 == 0 && ((uintptr_t)g.a[j].p & 15) == 0));
+  if (vec) stream_add_norm_kernel<4><<<(unsigned)tokens, STREAM_THREADS, 0, st>>>(g);
+  else stream_add_norm_kernel<1><<<(unsigned)tokens, STREAM_THREADS, 0, st>>>(g);
   return CB_LAUNCH_CHECK();
 }
 
@@ -1296,10 +1387,13 @@ int cb_latent_kv_write(const void* z, int64_t ldz, const void* w, int w_dtype, f
 int cb_clamped_glu(const void* gu, void* out, int64_t rows, int I, float limit, float alpha, int dtype,
                    const int64_t* row_limit, cudaStream_t st) {
   if (rows == 0 || I == 0) return 0;
-  const int64_t total = rows * I;
-  const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   CB_DISPATCH_FLOAT(dtype, T, {
-    clamped_glu_kernel<T><<<grid, 256, 0, st>>>((const T*)gu, (T*)out, rows, I, limit, alpha, row_limit);
+    constexpr int V = 16 / sizeof(T);
+    const bool vec = I % V == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    const int64_t total = rows * (vec ? I / V : I);
+    const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (vec) clamped_glu_kernel<T, V><<<grid, 256, 0, st>>>((const T*)gu, (T*)out, rows, I, limit, alpha, row_limit);
+    else clamped_glu_kernel<T, 1><<<grid, 256, 0, st>>>((const T*)gu, (T*)out, rows, I, limit, alpha, row_limit);
   });
   return CB_LAUNCH_CHECK();
 }
@@ -1334,7 +1428,7 @@ int cb_paged_bias_attention(const void* q, int64_t ldq, const void* k_cache, con
   return CB_LAUNCH_CHECK();
 }
 
-// 16-bit dtypes, widths that are multiples of 8 and at most 128: the tensor-core kernel.  `chunk` > 0 (a multiple of 64)
+// 16-bit dtypes, widths that are multiples of 8 and at most 256: the tensor-core kernel.  `chunk` > 0 (a multiple of 64)
 // splits the keys over CTAs; part_o [tokens x heads x max_splits x vdim] and part_ml [.. x 2] are its fp32 workspace.
 int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
                                 const int* block_tables, const int* cu_q, const int* ctx_len, const int* token_pos,
@@ -1343,7 +1437,7 @@ int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache,
                                 int block_size, int max_blocks, float scale, int sink, int chunk, int max_splits,
                                 float* part_o, float* part_ml, int dtype, cudaStream_t st) {
   if (nseq == 0 || max_q == 0) return 0;
-  if (heads % kv_heads != 0 || dim % 8 != 0 || vdim % 8 != 0 || dim > 128 || vdim > 128 || (ldq & 7) || ((uintptr_t)q & 15) ||
+  if (heads % kv_heads != 0 || dim % 8 != 0 || vdim % 8 != 0 || dim > 256 || vdim > 256 || (ldq & 7) || ((uintptr_t)q & 15) ||
       (ldv & 7) || ldv < vdim ||
       chunk % MMA_BN != 0)
     return (int)cudaErrorInvalidValue;
@@ -1361,7 +1455,13 @@ int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache,
   CB_DISPATCH_HALF(dtype, T, {
     if (dmax <= 32) { CB_ATT_MMA(T, 32); }
     else if (dmax <= 64) { CB_ATT_MMA(T, 64); }
-    else { CB_ATT_MMA(T, 128); }
+    else if (dmax <= 128) { CB_ATT_MMA(T, 128); }
+    else {                                               // 129..256 wide rows: one m16 tile per warp, one CTA per SM
+      return launch_attention_mma<T, 256, 1>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table,
+                                             lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,
+                                             ldv, block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml,
+                                             st);
+    }
   });
 #undef CB_ATT_MMA
   return CB_LAUNCH_CHECK();

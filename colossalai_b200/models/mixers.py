@@ -162,8 +162,10 @@ class LatentAttention(_MixerBase):
         assert spec.rot_dims in (0, r) and r % 2 == 0, "the decoupled key part is rotated as a whole"
         self.in_proj = nn.Linear(cfg.hidden_size, H * (d + r) + R + r, bias=False)       # q | latent | key part
         self.dkv_norm_weight = nn.Parameter(torch.ones(R))
-        self.uk = nn.Parameter(torch.zeros(H, d, R))              # U_n: latent -> unrotated key of head n
-        self.uv = nn.Parameter(torch.zeros(H, dv, R))             # V_n: latent -> value of head n
+        self.uk = nn.Parameter(torch.empty(H, d, R))              # U_n: latent -> unrotated key of head n
+        self.uv = nn.Parameter(torch.empty(H, dv, R))             # V_n: latent -> value of head n
+        nn.init.normal_(self.uk, std=cfg.initializer_range)
+        nn.init.normal_(self.uv, std=cfg.initializer_range)
         self.o_proj = nn.Linear(H * dv, cfg.hidden_size, bias=False)
         self.scale = spec.scale if spec.scale is not None else (d + r) ** -0.5
 

@@ -72,7 +72,8 @@ def moe_forward_gather(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Te
     k = topk_idx.shape[1]
     flat_idx = topk_idx.reshape(-1)
     order = torch.argsort(flat_idx, stable=True)
-    counts = torch.bincount(flat_idx, minlength=num_experts)
+    counts = torch.zeros(num_experts, dtype=torch.int64, device=x.device).scatter_add_(
+        0, flat_idx, torch.ones_like(flat_idx))                        # (bincount would read its size back to the host)
     ys = experts(x.index_select(0, order // k), counts)                # [T*k, H] grouped by expert
     inv = torch.empty_like(order)
     inv[order] = torch.arange(T * k, device=x.device)

@@ -511,7 +511,7 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     the bucket of the distance (`bucket_starts` [buckets] int32: smallest distance of each bucket); `sink` adds a key of
     score 0 without a value to the softmax.  Returns [T, heads x vdim].
 
-    Two kernels: 16-bit inputs whose head widths are multiples of 8 up to 128 run on tensor cores (`lut` = `bucket_lut`
+    Two kernels: 16-bit inputs whose head widths are multiples of 8 up to 256 run on tensor cores (`lut` = `bucket_lut`
     of the same buckets; built here when absent); everything else - fp32 above all - takes the exact CUDA-core kernel.
     `tensor_cores` forces the choice."""
     T = q.shape[0]
@@ -525,14 +525,14 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
             raise NotImplementedError("paged_bias_attention: value width above 512 is not supported")
         assert q.stride(1) == 1 and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
         out = torch.empty(T, heads * vdim, dtype=q.dtype, device=q.device)
-        mma_ok = (q.dtype in (torch.bfloat16, torch.float16) and dim % 8 == 0 and vdim % 8 == 0 and dim <= 128
-                  and vdim <= 128 and nb <= 255 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and ldv % 8 == 0)
+        mma_ok = (q.dtype in (torch.bfloat16, torch.float16) and dim % 8 == 0 and vdim % 8 == 0 and dim <= 256
+                  and vdim <= 256 and nb <= 255 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and ldv % 8 == 0)
         if tensor_cores is None:
             tensor_cores = mma_ok
         if tensor_cores:
             if not mma_ok:
                 raise ValueError("paged_bias_attention: the tensor-core kernel needs 16-bit inputs and head widths "
-                                 "that are multiples of 8 up to 128")
+                                 "that are multiples of 8 up to 256")
             if nb and lut is None:
                 lut = bucket_lut(bucket_starts.tolist()).to(q.device)
             # few CTAs (decode steps): split the keys so that about two waves of CTAs run, join the parts afterwards

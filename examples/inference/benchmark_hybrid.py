@@ -1,8 +1,11 @@
 """Serving throughput of a hybrid decoder (Gopunex layers: channel-wise delta rule / bias+sink attention / lightning
 attention) beside a Llama of equal width, depth and head sizes, both with random weights through `LLMEngine`, plus the
-time of every mixer kernel alone against its roofline.
+time of every mixer kernel alone against its roofline.  `--family palilix` runs the Palilix family (parallel layers with
+retention / latent attention, dense and routed feed-forwards, a looped span) beside Gopunex, the closest served family,
+at equal width and number of layer runs, and its kernels beside their like kernels.
 
     python examples/inference/benchmark_hybrid.py [--sizes 2048x8,4096x4] [--batch 8] [--in_len 2048] [--out_len 64]
+                                                  [--family gopunex|palilix]
 
 Also reachable as `python bench.py --workload hybrid-serve`.  One JSON line per (size, family) and one per kernel.
 Timing: CUDA events on the launching stream after warm-up; the kernel timings write a 256 MB buffer between runs (L2
@@ -20,7 +23,7 @@ sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."
 from colossalai_b200.inference import GenerationConfig, InferenceConfig  # noqa: E402
 from colossalai_b200.inference.core.llm_engine import LLMEngine  # noqa: E402
 from colossalai_b200.models import build_model  # noqa: E402
-from colossalai_b200.models.config import LayerSpec, MixerSpec, ModelConfig  # noqa: E402
+from colossalai_b200.models.config import ExpertFFSpec, LayerSpec, MixerSpec, ModelConfig  # noqa: E402
 
 ROOT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..")
 
@@ -44,6 +47,26 @@ def hybrid_config(width: int, layers: int, vocab: int = 32000) -> ModelConfig:
     return ModelConfig(model_type="gopunex", vocab_size=vocab, hidden_size=width, intermediate_size=4 * width,
                        layer_specs=specs, norm_eps=1e-5, hidden_act="relu2", glu=False, pos_type="none",
                        norm_placement="sublayer_out", residual_mult=0.7, norm_weight_offset=1.0, fp32_residual=True,
+                       max_position_embeddings=1 << 20)
+
+
+def palilix_config(width: int, runs: int, vocab: int = 32000, kv_rank: int = 192, rot: int = 64) -> ModelConfig:
+    """`runs` layer runs: runs - 2 distinct layers of which the second and third run twice.  Heads of 128 channels;
+    latent rows of kv_rank + rot = 256 columns; every other layer has routed experts (8, top 2) with a shared expert."""
+    H, d = width // 128, 128
+    ret = MixerSpec(kind="retention", heads=H, dim=d, vdim=d, decay=[1.0 - 2.0 ** -(5 + 3 * i / H) for i in range(H)],
+                    rot_dims=64, rot_base=1e6)
+    lat = MixerSpec(kind="latent", heads=H, kv_heads=1, dim=d - rot, rot_dim=rot, rot_dims=rot, vdim=d, kv_rank=kv_rank,
+                    rot_base=5e5, scale=d ** -0.5)
+    moe = ExpertFFSpec(experts=8, top=2, ff=width, limit=7.0, shared_ff=2 * width, shared_limit=7.0)
+    order = [(ret, None), (ret, moe), (lat, moe), (lat, None)]
+    n = max(runs - 2, 3)
+    specs = [LayerSpec(mixer=order[i % 4][0], ff=None if order[i % 4][1] else 4 * width, moe=order[i % 4][1])
+             for i in range(n)]
+    return ModelConfig(model_type="palilix", vocab_size=vocab, hidden_size=width, intermediate_size=4 * width,
+                       layer_specs=specs, norm_eps=1e-5, norm_type="layer", norm_bias=False, hidden_act="gelu_tanh",
+                       glu=False, pos_type="none", parallel_block=True, fp32_residual=True, embed_scale=1.0,
+                       logit_scale=1.0, logit_softcap=30.0, loop_start=1, loop_stop=3, loop_times=2,
                        max_position_embeddings=1 << 20)
 
 
@@ -104,7 +127,7 @@ def serve(cfg: ModelConfig, batch: int, in_len: int, out_len: int, cuda_graph: b
     tp, td, steps = run()
     n_params = sum(p.numel() for p in model.parameters())
     out = {"family": cfg.model_type, "width": cfg.hidden_size, "layers": cfg.num_hidden_layers, "params": n_params,
-           "batch": batch, "in_len": in_len, "out_len": out_len, "cuda_graph": cuda_graph, "prefill_ms": tp,
+           "layer_runs": cfg.num_cache_layers, "batch": batch, "in_len": in_len, "out_len": out_len, "cuda_graph": cuda_graph, "prefill_ms": tp,
            "prefill_tokens_per_s": batch * in_len / (tp / 1e3), "decode_ms_per_step": td / max(steps, 1),
            "decode_tokens_per_s": batch * steps / (td / 1e3), "our_kernel_launches": loader.launch_counter.count}
     del eng, model
@@ -203,6 +226,108 @@ def kernels(width: int, batch: int, in_len: int) -> list:
     return rows
 
 
+def kernels_palilix(width: int, batch: int, in_len: int, kv_rank: int = 192, rot: int = 64) -> list:
+    """Every kernel of the Palilix layers alone at one layer's sizes beside its like kernel of the closest families."""
+    from colossalai_b200 import ops
+    from colossalai_b200.ops import inference as iops
+    from colossalai_b200.ops import mixers as M
+    from colossalai_b200.ops.moe import gather_combine
+
+    hbm, tflops, src = peaks()
+    dev, dt = "cuda", torch.bfloat16
+    H, d, bs = width // 128, 128, 64
+    G = max(H // 4, 1)
+    Dk = kv_rank + rot
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    rows = []
+
+    def rec(name, phase, ms, bytes_, flops, like=""):
+        ideal = max(bytes_ / hbm, flops / tflops) * 1e3
+        rows.append({"kernel": name, "phase": phase, "width": width, "ms": ms, "roofline_ms": ideal,
+                     "frac_of_" + src + "_roofline": ideal / ms, "bound": "hbm" if bytes_ / hbm > flops / tflops else "tensor",
+                     "like": like})
+
+    for phase, q_len, ctx in (("prefill", in_len, 0), ("decode", 1, in_len)):
+        T = batch * q_len
+        meta = M.RaggedMeta.build([q_len] * batch, [ctx] * batch, list(range(batch)), dev)
+        x = lambda c: torch.randn(T, c, device=dev, dtype=dt)
+        # stream sum + layer norm  |  like: Gopunex norm + residual, Llama fused norm
+        xs, y1, y2 = torch.randn(T, width, device=dev), x(width), x(width)
+        w = torch.ones(width, device=dev, dtype=dt)
+        ms = _time(lambda: M.stream_add_norm(xs, [y1, y2], weight=w, eps=1e-5, kind="layer"), flush)
+        rec("stream_add_norm(2 addends, layer norm)", phase, ms, T * width * (4 + 4 + 2 + 2 + 2), 0, like="rmsnorm_residual")
+        ms = _time(lambda: M.rms_norm_residual(xs, y1, w, 1e-5, 0.7, 1.0), flush)
+        rec("gopunex:rmsnorm_residual", phase, ms, T * width * (4 + 4 + 2 + 2), 0)
+        ms = _time(lambda: ops.rms_norm(y1, w, 1e-5, y2), flush)
+        rec("llama:rmsnorm_fwd(+residual)", phase, ms, T * width * 2 * 4, 0)
+        # retention scan with rotary positions  |  like: the same scan without them (lightning attention)
+        S = torch.zeros(batch, H, d, d, device=dev)
+        state_bytes = 2 * S.numel() * 4
+        q, k, v = x(H * d) * 0.1, x(H * d) * 0.1, x(H * d)
+        dec = torch.full((H,), 0.97, device=dev)
+        table = M.rotary_table(ctx + q_len, 64, 1e6, dev)
+        ms = _time(lambda: M.state_scan_decay(q, k, v, dec, S, meta, H, d, d, act_silu=False, rot_table=table, rot_dims=64,
+                                              k_scale=d ** -0.5), flush)
+        rec("state_scan_decay+rotary", phase, ms, T * (3 * H * d * 2 + H * d * 4) + state_bytes, 4.0 * T * H * d * d,
+            like="state_scan_decay")
+        ms = _time(lambda: M.state_scan_decay(q, k, v, dec, S, meta, H, d, d), flush)
+        rec("gopunex:state_scan_decay", phase, ms, T * (3 * H * d * 2 + H * d * 4) + state_bytes, 4.0 * T * H * d * d)
+        o, gate, wn = torch.randn(T, H * d, device=dev), x(H * d), torch.ones(d, device=dev, dtype=dt)
+        ms = _time(lambda: M.gated_group_rms_norm(o, None, gate, d, 1e-5, dt, gate_act="silu"), flush)
+        rec("gated_group_rmsnorm(silu)", phase, ms, T * H * d * (4 + 2 + 2), 0, like="gated_group_rmsnorm")
+        ms = _time(lambda: M.gated_group_rms_norm(o, wn, gate, d, 1e-5, dt), flush)
+        rec("gopunex:gated_group_rmsnorm", phase, ms, T * H * d * (4 + 2 + 2), 0)
+        # latent attention: cache rows, query rotation, attention over the rows
+        L = ctx + q_len
+        per = (L + bs - 1) // bs
+        cache = torch.randn(batch * per, bs, 1, Dk, device=dev, dtype=dt)
+        tables = torch.arange(batch * per, dtype=torch.int32, device=dev).view(batch, per)
+        z, nw = x(Dk), torch.ones(kv_rank, device=dev, dtype=dt)
+        tab_r = M.rotary_table(L, rot, 5e5, dev)
+        ms = _time(lambda: M.latent_kv_write(z, nw, 1e-5, kv_rank, tab_r, cache, tables, meta), flush)
+        rec("latent_kv_write", phase, ms, 2 * T * Dk * 2, 0, like="paged_kv_write_mix")
+        kc = torch.randn(batch * per, bs, G, d, device=dev, dtype=dt)
+        vc = torch.randn(batch * per, bs, G, d, device=dev, dtype=dt)
+        kk, vv = x(G * d), x(G * d)
+        ms = _time(lambda: M.paged_kv_write_mix(kk, vv, kc, vc, tables, meta), flush)
+        rec("gopunex:paged_kv_write_mix", phase, ms, 2 * T * 2 * G * d * 2, 0)
+        qs, qa = x(H * d), torch.empty(T, H * Dk, device=dev, dtype=dt)
+        ms = _time(lambda: M.rotary_half(qs, qa, H, d, d - rot, Dk, kv_rank, rot, rot, tab_r, meta.token_pos), flush)
+        rec("rotary_half(q part)", phase, ms, 2 * T * H * rot * 2, 0, like="rope_qkv")
+        qa.normal_()
+        ms = _time(lambda: M.paged_bias_attention(qa, cache, cache, tables, meta, d ** -0.5, vdim=kv_rank), flush)
+        kv_bytes = batch * L * Dk * 2
+        att_flops = 2.0 * batch * H * (Dk + kv_rank) * (q_len * ctx + q_len * (q_len + 1) / 2)
+        rec("latent_attention", phase, ms, kv_bytes + T * H * (Dk + kv_rank) * 2, att_flops,
+            like="paged_bias_attention")
+        qg = x(H * d)
+        rel = torch.randn(32, H, device=dev)
+        starts_host = M.log_bucket_starts(32, 512.0)
+        starts = torch.tensor(starts_host, dtype=torch.int32, device=dev)
+        lut = M.bucket_lut(starts_host).to(dev)
+        ms = _time(lambda: M.paged_bias_attention(qg, kc, vc, tables, meta, d ** -0.5, rel, starts, True, lut=lut), flush)
+        g_bytes = 2 * batch * L * G * d * 2 + 2 * T * H * d * 2
+        g_flops = 4.0 * batch * H * d * (q_len * ctx + q_len * (q_len + 1) / 2)
+        rec("gopunex:paged_bias_attention", phase, ms, g_bytes, g_flops)
+        if phase == "decode":
+            lens = torch.full((batch,), L, dtype=torch.int32, device=dev)
+            ms = _time(lambda: iops.paged_decode_attention(qg.view(T, H, d), kc, vc, tables, lens, d ** -0.5), flush)
+            rec("llama:paged_decode_attention", phase, ms, g_bytes, g_flops)
+        # experts: clamped gated unit (top 2 of every token), fp32 gather-combine
+        I = width
+        gu = x(2 * I).repeat(2, 1)
+        ms = _time(lambda: ops.clamped_glu(gu, 7.0, 1.702), flush)
+        rec("clamped_glu", phase, ms, 2 * T * 3 * I * 2, 0, like="glu_fwd(silu)")
+        ms = _time(lambda: ops.glu(gu, "silu"), flush)
+        rec("llama:glu_fwd(silu)", phase, ms, 2 * T * 3 * I * 2, 0)
+        ys = x(width).repeat(2, 1)
+        row_of = torch.randperm(2 * T, device=dev).view(T, 2)
+        wts = torch.rand(T, 2, device=dev)
+        ms = _time(lambda: gather_combine(ys, row_of, wts), flush)
+        rec("moe_gather_combine", phase, ms, T * width * (2 * 2 + 4), 0)
+    return rows
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--sizes", default="2048x8,4096x4", help="width x layers, comma separated")
@@ -210,6 +335,8 @@ def main(argv=None):
     ap.add_argument("--in_len", type=int, default=2048)
     ap.add_argument("--out_len", type=int, default=32)
     ap.add_argument("--cuda_graph", action="store_true", help="also run both families with CUDA-graph decode steps")
+    ap.add_argument("--family", default="gopunex", choices=["gopunex", "palilix"],
+                    help="gopunex: the hybrid decoder beside Llama (default).  palilix: the Palilix family beside Gopunex")
     ap.add_argument("--no-kernels", action="store_true")
     ap.add_argument("--no-serve", action="store_true")
     args = ap.parse_args(argv)
@@ -218,10 +345,12 @@ def main(argv=None):
         width, layers = (int(z) for z in size.split("x"))
         if not args.no_serve:
             for graph in ([False, True] if args.cuda_graph else [False]):
-                for cfg in (hybrid_config(width, layers), llama_config(width, layers)):
+                pair = (hybrid_config(width, layers), llama_config(width, layers)) if args.family == "gopunex" else \
+                    (palilix_config(width, layers), hybrid_config(width, layers))
+                for cfg in pair:
                     print(json.dumps(serve(cfg, args.batch, args.in_len, args.out_len, graph)), flush=True)
         if not args.no_kernels:
-            for row in kernels(width, args.batch, args.in_len):
+            for row in (kernels if args.family == "gopunex" else kernels_palilix)(width, args.batch, args.in_len):
                 print(json.dumps(row), flush=True)
 
 

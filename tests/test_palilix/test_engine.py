@@ -44,10 +44,10 @@ def _tier(tier):
         pytest.skip("needs a CUDA device")
 
 
-def _engine(path, dtype=torch.float32, slots=3, pool_tokens=512, block_size=8, budget=4096, max_out=8):
+def _engine(path, dtype=torch.float32, slots=3, pool_tokens=512, block_size=8, budget=4096, max_out=8, graphs=False):
     cfg = InferenceConfig(dtype=dtype, max_batch_size=slots, max_input_len=pool_tokens, max_output_len=max_out,
                           block_size=block_size, max_cache_tokens=pool_tokens, max_num_batched_tokens=budget,
-                          use_cuda_graph=False)
+                          use_cuda_graph=graphs)
     return LLMEngine(path, inference_config=cfg)
 
 
@@ -225,6 +225,27 @@ def test_greedy_generation_through_the_scheduler(tmp_path, tier):
             seq.append(int(logits.argmax()))
         assert full == seq
     assert eng.request_handler.state_manager.num_available_slots == 2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,dtype", [("looped", torch.bfloat16), ("plain-ones", torch.bfloat16),
+                                        ("all-looped", torch.bfloat16)])
+def test_graph_replayed_decode_steps_match_eager_ones(tmp_path, name, dtype):
+    """Decode steps replayed from CUDA graphs (fixed layout buffer, worst-case launch shapes) against eager steps:
+    three sequences of unequal length decode side by side, one ends early so the batch size changes."""
+    _tier("gpu")
+    path, cfg, W = _model(tmp_path, name, seed=17)
+    lens = {"a": 70, "b": 9, "c": 33}
+    prompts = {r: _tokens(n, cfg["vocab"], 40 + i) for i, (r, n) in enumerate(lens.items())}
+    schedule = [[("a", 40), ("b", 3), ("c", 20)]] + [[("a", 1), ("b", 1), ("c", 1)]] * 6 + \
+        [[("a", 1), ("c", 1)]] * 7 + [[("a", 1)]] * 17
+    eager = _run(_engine(path, dtype=dtype, block_size=16), schedule, prompts)
+    eng = _engine(path, dtype=dtype, block_size=16, graphs=True)
+    assert sorted(eng.ragged_graphs) == [1, 2]            # the ladder of batch sizes up to three slots
+    replayed = _run(eng, schedule, prompts)
+    for r in prompts:
+        _check(replayed[r], eager[r], 3e-2)
+        _check(replayed[r], O.forward(cfg, W, prompts[r]), 8e-2)
 
 
 @pytest.mark.parametrize("tier", TIERS)
