@@ -525,136 +525,134 @@ __global__ void __launch_bounds__(256) rmsnorm_f32in_kernel(const float* __restr
 }
 
 // ------------------------------------------------------------------------------------------------ stream sums + norm
-// One CTA per token row of the fp32 residual stream: x += ((a0 + a1) + a2 + a3) + row, the addends in their own dtypes
-// (fp32 or 16-bit), summed among themselves first; then, with NORM = 1 / 2, h = cast(norm(x) * (offset + w)) where the
-// norm is x / sqrt(mean x^2 + eps) or (x - mean) / sqrt(mean (x - mean)^2 + eps).  The row stays in registers between the
-// passes (up to STREAM_ITEMS values per thread; wider rows are re-read from x, which the same thread wrote).
-constexpr int STREAM_THREADS = 256, STREAM_ITEMS = 8;
+// One CTA per token row of the fp32 residual stream: x += ((a0 + a1) + a2 + a3) + row, every addend either fp32 or the
+// 16-bit type T, summed among themselves first; then, with NORM = 1 / 2, h = cast(norm(x) * (offset + w)) where the norm
+// is x / sqrt(mean x^2 + eps) or (x - mean) / sqrt(mean (x - mean)^2 + eps) (w and h: fp32 or T).  The row stays in
+// registers between the passes: ITEMS x VEC values per thread, chosen by the launcher from the row width (rows wider
+// than 8 x VEC x threads re-read the rest from x, which the same thread wrote).  Every load of the row is issued before
+// the first store.
+constexpr int STREAM_THREADS = 256;
 
-struct StreamAddend { const void* p; int64_t ld; int dtype; };
 struct StreamArgs {
   float* x;
-  StreamAddend a[4];
+  const void* a[4];
+  int64_t ld[4];
+  int a_f32[4];                 // addend j is fp32 (else T)
   const float* row;
   const void* w;
-  int w_dtype;
+  int w_f32;
   void* h;
-  int h_dtype;
-  int W, norm;
+  int h_f32;
+  int W;
   float eps, offset;
 };
 
-// VEC consecutive values of a row in any float dtype (VEC = 4: one 16-byte or 8-byte access)
-template <int VEC> CB_DEVICE void load_any(const void* p, int dtype, int64_t i, float (&v)[VEC]) {
-  if (dtype == CB_F32) {
+template <typename T, int VEC> CB_DEVICE void load_vec(const void* p, bool f32, int64_t i, float (&v)[VEC]) {
+  if (f32) {
     struct alignas(4 * VEC) P { float e[VEC]; };
     const P a = *reinterpret_cast<const P*>((const float*)p + i);
 #pragma unroll
     for (int e = 0; e < VEC; ++e) v[e] = a.e[e];
-  } else if (dtype == CB_BF16) {
-    struct alignas(2 * VEC) P { __nv_bfloat16 e[VEC]; };
-    const P a = *reinterpret_cast<const P*>((const __nv_bfloat16*)p + i);
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) v[e] = __bfloat162float(a.e[e]);
   } else {
-    struct alignas(2 * VEC) P { __half e[VEC]; };
-    const P a = *reinterpret_cast<const P*>((const __half*)p + i);
+    struct alignas(sizeof(T) * VEC) P { T e[VEC]; };
+    const P a = *reinterpret_cast<const P*>((const T*)p + i);
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) v[e] = __half2float(a.e[e]);
+    for (int e = 0; e < VEC; ++e) v[e] = to_f32<T>(a.e[e]);
   }
 }
-template <int VEC> CB_DEVICE void store_any(void* p, int dtype, int64_t i, const float (&v)[VEC]) {
-  if (dtype == CB_F32) {
+template <typename T, int VEC> CB_DEVICE void store_vec(void* p, bool f32, int64_t i, const float (&v)[VEC]) {
+  if (f32) {
     struct alignas(4 * VEC) P { float e[VEC]; };
     P a;
 #pragma unroll
     for (int e = 0; e < VEC; ++e) a.e[e] = v[e];
     *reinterpret_cast<P*>((float*)p + i) = a;
-  } else if (dtype == CB_BF16) {
-    struct alignas(2 * VEC) P { __nv_bfloat16 e[VEC]; };
-    P a;
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) a.e[e] = __float2bfloat16_rn(v[e]);
-    *reinterpret_cast<P*>((__nv_bfloat16*)p + i) = a;
   } else {
-    struct alignas(2 * VEC) P { __half e[VEC]; };
+    struct alignas(sizeof(T) * VEC) P { T e[VEC]; };
     P a;
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) a.e[e] = __float2half_rn(v[e]);
-    *reinterpret_cast<P*>((__half*)p + i) = a;
+    for (int e = 0; e < VEC; ++e) a.e[e] = from_f32<T>(v[e]);
+    *reinterpret_cast<P*>((T*)p + i) = a;
   }
 }
 
-// new stream values of VEC columns starting at i: x + (sum of the addends + row), written back when anything was added
-template <int VEC> CB_DEVICE void stream_take(const StreamArgs& g, float* xr, int64_t t, int i, float (&xv)[VEC]) {
+// new stream values of VEC columns starting at i: x + (sum of the addends + row)
+template <typename T, int VEC> CB_DEVICE void stream_take(const StreamArgs& g, const float* xr, int64_t t, int i,
+                                                          float (&xv)[VEC]) {
   float add[VEC];
   bool any = false;
 #pragma unroll
   for (int j = 0; j < 4; ++j)
-    if (g.a[j].p != nullptr) {
+    if (g.a[j] != nullptr) {
       float v[VEC];
-      load_any<VEC>(g.a[j].p, g.a[j].dtype, t * g.a[j].ld + i, v);
+      load_vec<T, VEC>(g.a[j], g.a_f32[j] != 0, t * g.ld[j] + i, v);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) add[e] = any ? add[e] + v[e] : v[e];
       any = true;
     }
   if (g.row != nullptr) {
     float v[VEC];
-    load_any<VEC>(g.row, CB_F32, i, v);
+    load_vec<T, VEC>(g.row, true, i, v);
 #pragma unroll
     for (int e = 0; e < VEC; ++e) add[e] = any ? add[e] + v[e] : v[e];
     any = true;
   }
-  load_any<VEC>(xr, CB_F32, i, xv);
+  load_vec<T, VEC>(xr, true, i, xv);
   if (any) {
 #pragma unroll
     for (int e = 0; e < VEC; ++e) xv[e] += add[e];
-    store_any<VEC>(xr, CB_F32, i, xv);
   }
 }
 
-template <int VEC>
-__global__ void __launch_bounds__(STREAM_THREADS) stream_add_norm_kernel(StreamArgs g) {
+template <typename T, int VEC, int ITEMS, int NORM>
+__global__ void __launch_bounds__(STREAM_THREADS, ITEMS <= 2 ? 6 : (ITEMS <= 4 ? 4 : 3)) stream_add_norm_kernel(StreamArgs g) {
   constexpr int STEP = STREAM_THREADS * VEC;
   __shared__ float red[64];
   const int64_t t = blockIdx.x;
   const int W = g.W;
   float* xr = g.x + t * W;
-  float keep[STREAM_ITEMS][VEC];
+  const bool any = g.a[0] != nullptr || g.a[1] != nullptr || g.a[2] != nullptr || g.a[3] != nullptr || g.row != nullptr;
+  float keep[ITEMS][VEC];
   float sum[1] = {0.f};
   const int i0 = threadIdx.x * VEC;
 #pragma unroll
-  for (int n = 0; n < STREAM_ITEMS; ++n) {
+  for (int n = 0; n < ITEMS; ++n) {
     const int i = i0 + n * STEP;
     if (i < W) {
-      stream_take<VEC>(g, xr, t, i, keep[n]);
+      stream_take<T, VEC>(g, xr, t, i, keep[n]);
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) sum[0] += g.norm == 1 ? keep[n][e] * keep[n][e] : keep[n][e];
+      for (int e = 0; e < VEC; ++e) sum[0] += NORM == 1 ? keep[n][e] * keep[n][e] : keep[n][e];
     }
   }
-  for (int i = i0 + STREAM_ITEMS * STEP; i < W; i += STEP) {       // rows wider than the registers hold
-    float xv[VEC];
-    stream_take<VEC>(g, xr, t, i, xv);
+  if (any) {
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) sum[0] += g.norm == 1 ? xv[e] * xv[e] : xv[e];
+    for (int n = 0; n < ITEMS; ++n)
+      if (i0 + n * STEP < W) store_vec<T, VEC>(xr, true, i0 + n * STEP, keep[n]);
   }
-  if (g.norm == 0) return;
+  for (int i = i0 + ITEMS * STEP; i < W; i += STEP) {       // rows wider than the registers hold
+    float xv[VEC];
+    stream_take<T, VEC>(g, xr, t, i, xv);
+    if (any) store_vec<T, VEC>(xr, true, i, xv);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) sum[0] += NORM == 1 ? xv[e] * xv[e] : xv[e];
+  }
+  if (NORM == 0) return;
   block_sum<1>(sum, red);
   float mean = 0.f, r;
-  if (g.norm == 1) {
+  if (NORM == 1) {
     r = 1.f / sqrtf(sum[0] / (float)W + g.eps);
   } else {
     mean = sum[0] / (float)W;
     float sq[1] = {0.f};
 #pragma unroll
-    for (int n = 0; n < STREAM_ITEMS; ++n)
+    for (int n = 0; n < ITEMS; ++n)
       if (i0 + n * STEP < W) {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) { const float d = keep[n][e] - mean; sq[0] = fmaf(d, d, sq[0]); }
       }
-    for (int i = i0 + STREAM_ITEMS * STEP; i < W; i += STEP) {
+    for (int i = i0 + ITEMS * STEP; i < W; i += STEP) {
       float xv[VEC];
-      load_any<VEC>(xr, CB_F32, i, xv);
+      load_vec<T, VEC>(xr, true, i, xv);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) { const float d = xv[e] - mean; sq[0] = fmaf(d, d, sq[0]); }
     }
@@ -663,46 +661,70 @@ __global__ void __launch_bounds__(STREAM_THREADS) stream_add_norm_kernel(StreamA
   }
   auto emit = [&](int i, const float (&xv)[VEC]) {
     float wv[VEC], y[VEC];
-    if (g.w != nullptr) load_any<VEC>(g.w, g.w_dtype, i, wv);
+    if (g.w != nullptr) load_vec<T, VEC>(g.w, g.w_f32 != 0, i, wv);
 #pragma unroll
     for (int e = 0; e < VEC; ++e) y[e] = (xv[e] - mean) * r * (g.offset + (g.w != nullptr ? wv[e] : 1.f));
-    store_any<VEC>(g.h, g.h_dtype, t * W + i, y);
+    store_vec<T, VEC>(g.h, g.h_f32 != 0, t * W + i, y);
   };
 #pragma unroll
-  for (int n = 0; n < STREAM_ITEMS; ++n)
+  for (int n = 0; n < ITEMS; ++n)
     if (i0 + n * STEP < W) emit(i0 + n * STEP, keep[n]);
-  for (int i = i0 + STREAM_ITEMS * STEP; i < W; i += STEP) {
+  for (int i = i0 + ITEMS * STEP; i < W; i += STEP) {
     float xv[VEC];
-    load_any<VEC>(xr, CB_F32, i, xv);
+    load_vec<T, VEC>(xr, true, i, xv);
     emit(i, xv);
   }
 }
 
+template <typename T, int NORM> int launch_stream_add_norm(const StreamArgs& g, int64_t tokens, bool vec, cudaStream_t st) {
+  const unsigned grid = (unsigned)tokens;
+  if (!vec) stream_add_norm_kernel<T, 1, 8, NORM><<<grid, STREAM_THREADS, 0, st>>>(g);
+  else if (g.W <= 2 * 4 * STREAM_THREADS) stream_add_norm_kernel<T, 4, 2, NORM><<<grid, STREAM_THREADS, 0, st>>>(g);
+  else if (g.W <= 4 * 4 * STREAM_THREADS) stream_add_norm_kernel<T, 4, 4, NORM><<<grid, STREAM_THREADS, 0, st>>>(g);
+  else stream_add_norm_kernel<T, 4, 8, NORM><<<grid, STREAM_THREADS, 0, st>>>(g);
+  return CB_LAUNCH_CHECK();
+}
+
 // ------------------------------------------------------------------------------------------------ rotary positions
-// table [positions, dims] fp32: cos(p f_i) for i < dims / 2, then sin(p f_i).  One thread per (token, head, channel of
-// the copied width): channel i < dims / 2 pairs with i + dims / 2; channels at dims and above are copied.
-template <typename TI, typename TO>
-__global__ void __launch_bounds__(256) rotary_half_kernel(const TI* __restrict__ src, int64_t lds, TO* __restrict__ dst,
+// table [positions, dims] fp32: cos(p f_i) for i < dims / 2, then sin(p f_i).  A work item is VEC consecutive channels of
+// one (token, head): in the rotated part the item takes channels i.. of the first half TOGETHER with their partners
+// i + dims / 2.. (two loads, two stores of VEC values); behind the rotated part it copies.  VEC = 8 (16-byte accesses of
+// 16-bit data) when every offset, stride and width allows it, else 1.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) rotary_half_kernel(const T* __restrict__ src, int64_t lds, T* __restrict__ dst,
                                                           int64_t ldd, int64_t tokens, int heads, int src_hs, int src_off,
                                                           int dst_hs, int dst_off, int width, int dims,
                                                           const float* __restrict__ table,
                                                           const int* __restrict__ token_pos) {
-  const int64_t total = tokens * heads * width;
+  struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
   const int half = dims >> 1;
+  const int items = (half + (width - dims)) / VEC;          // per (token, head): pair groups, then copy groups
+  const int64_t total = tokens * heads * items;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(idx % width);
-    const int h = (int)((idx / width) % heads);
-    const int64_t t = idx / ((int64_t)width * heads);
-    const TI* s = src + t * lds + h * src_hs + src_off;
-    float y = to_f32<TI>(s[c]);
-    if (c < dims) {
+    const int it = (int)(idx % items);
+    const int h = (int)((idx / items) % heads);
+    const int64_t t = idx / ((int64_t)items * heads);
+    const T* s = src + t * lds + h * src_hs + src_off;
+    T* d = dst + t * ldd + h * dst_hs + dst_off;
+    const int c = it * VEC;
+    if (c < half) {
       const float* cs = table + (int64_t)token_pos[t] * dims;
-      const int i = c < half ? c : c - half;
-      const float co = cs[i], sn = cs[half + i];
-      const float other = to_f32<TI>(s[c < half ? c + half : c - half]);
-      y = c < half ? y * co - other * sn : y * co + other * sn;
+      const Pack u = *reinterpret_cast<const Pack*>(s + c);
+      const Pack v = *reinterpret_cast<const Pack*>(s + c + half);
+      Pack ou, ov;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float co = cs[c + e], sn = cs[half + c + e];
+        const float uf = to_f32<T>(u.v[e]), vf = to_f32<T>(v.v[e]);
+        ou.v[e] = from_f32<T>(uf * co - vf * sn);
+        ov.v[e] = from_f32<T>(vf * co + uf * sn);
+      }
+      *reinterpret_cast<Pack*>(d + c) = ou;
+      *reinterpret_cast<Pack*>(d + c + half) = ov;
+    } else {
+      const int cc = c + half;                               // the channel behind the rotated part
+      *reinterpret_cast<Pack*>(d + cc) = *reinterpret_cast<const Pack*>(s + cc);
     }
-    dst[t * ldd + h * dst_hs + dst_off + c] = from_f32<TO>(y);
   }
 }
 
@@ -1339,14 +1361,49 @@ int cb_stream_add_norm(float* x, const void* a0, int64_t ld0, int dt0, const voi
                        cudaStream_t st) {
   if (tokens == 0) return 0;
   if (norm < 0 || norm > 2 || (norm != 0 && h == nullptr)) return (int)cudaErrorInvalidValue;
-  StreamArgs g{x, {{a0, ld0, dt0}, {a1, ld1, dt1}, {a2, ld2, dt2}, {a3, ld3, dt3}}, row, w, w_dtype, h, h_dtype, W, norm,
-               eps, offset};
+  const void* ap[4] = {a0, a1, a2, a3};
+  const int64_t ld[4] = {ld0, ld1, ld2, ld3};
+  const int dts[4] = {dt0, dt1, dt2, dt3};
+  // the one 16-bit type among addends, weight and output (fp32 operands may be mixed with it freely)
+  int half_type = CB_F32;
+  StreamArgs g;
+  g.x = x;
+  for (int j = 0; j < 4; ++j) {
+    g.a[j] = ap[j];
+    g.ld[j] = ld[j];
+    g.a_f32[j] = dts[j] == CB_F32;
+    if (ap[j] != nullptr && dts[j] != CB_F32) {
+      if (half_type != CB_F32 && half_type != dts[j]) return (int)cudaErrorInvalidValue;
+      half_type = dts[j];
+    }
+  }
+  if (norm != 0) {
+    if (w != nullptr && w_dtype != CB_F32) {
+      if (half_type != CB_F32 && half_type != w_dtype) return (int)cudaErrorInvalidValue;
+      half_type = w_dtype;
+    }
+    if (h_dtype != CB_F32) {
+      if (half_type != CB_F32 && half_type != h_dtype) return (int)cudaErrorInvalidValue;
+      half_type = h_dtype;
+    }
+  }
+  g.row = row;
+  g.w = norm != 0 ? w : nullptr;
+  g.w_f32 = w_dtype == CB_F32;
+  g.h = h;
+  g.h_f32 = h_dtype == CB_F32;
+  g.W = W;
+  g.eps = eps;
+  g.offset = offset;
   // four columns per access when every row start and width allows it
   bool vec = W % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)row & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
              ((uintptr_t)h & 15) == 0;
-  for (int j = 0; j < 4; ++j) vec = vec && (g.a[j].p == nullptr || (g.a[j].ld % 4 == 0 && ((uintptr_t)g.a[j].p & 15) == 0));
-  if (vec) stream_add_norm_kernel<4><<<(unsigned)tokens, STREAM_THREADS, 0, st>>>(g);
-  else stream_add_norm_kernel<1><<<(unsigned)tokens, STREAM_THREADS, 0, st>>>(g);
+  for (int j = 0; j < 4; ++j) vec = vec && (ap[j] == nullptr || (ld[j] % 4 == 0 && ((uintptr_t)ap[j] & 15) == 0));
+  CB_DISPATCH_FLOAT(half_type, T, {
+    if (norm == 0) return launch_stream_add_norm<T, 0>(g, tokens, vec, st);
+    if (norm == 1) return launch_stream_add_norm<T, 1>(g, tokens, vec, st);
+    return launch_stream_add_norm<T, 2>(g, tokens, vec, st);
+  });
   return CB_LAUNCH_CHECK();
 }
 
@@ -1355,11 +1412,20 @@ int cb_rotary_half(const void* src, int64_t lds, void* dst, int64_t ldd, int64_t
                    int dst_dtype, cudaStream_t st) {
   if (tokens == 0 || heads == 0 || width == 0) return 0;
   if (dims > width || (dims & 1) || src_dtype != dst_dtype) return (int)cudaErrorInvalidValue;
-  const int64_t total = tokens * heads * width;
-  const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   CB_DISPATCH_FLOAT(src_dtype, T, {
-    rotary_half_kernel<T, T><<<grid, 256, 0, st>>>((const T*)src, lds, (T*)dst, ldd, tokens, heads, src_hs, src_off, dst_hs,
-                                                   dst_off, width, dims, table, token_pos);
+    constexpr int V = 16 / sizeof(T);
+    const int half = dims / 2;
+    const bool vec = half % V == 0 && (width - dims) % V == 0 && lds % V == 0 && ldd % V == 0 && src_hs % V == 0 &&
+                     src_off % V == 0 && dst_hs % V == 0 && dst_off % V == 0 && ((uintptr_t)src & 15) == 0 &&
+                     ((uintptr_t)dst & 15) == 0;
+    const int64_t total = tokens * heads * ((half + (width - dims)) / (vec ? V : 1));
+    const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+    if (vec)
+      rotary_half_kernel<T, V><<<grid, 256, 0, st>>>((const T*)src, lds, (T*)dst, ldd, tokens, heads, src_hs, src_off,
+                                                     dst_hs, dst_off, width, dims, table, token_pos);
+    else
+      rotary_half_kernel<T, 1><<<grid, 256, 0, st>>>((const T*)src, lds, (T*)dst, ldd, tokens, heads, src_hs, src_off,
+                                                     dst_hs, dst_off, width, dims, table, token_pos);
   });
   return CB_LAUNCH_CHECK();
 }

@@ -420,18 +420,29 @@ inline EpParams make_ep(const void* const* rows, const void* const* flags, const
   return p;
 }
 
-// out[t] = sum_j w[t, j] * rows[row_of[t, j]] in fp32, j ascending (a fixed order per token: no atomics).  One CTA per
-// token; rows in any float dtype.
-template <typename T>
+// out[t] = sum_j w[t, j] * rows[row_of[t, j]] in fp32, j ascending (a fixed order per token: no atomics).  A thread owns
+// VEC adjacent columns of a token (16-byte row reads when the width allows); rows in any float dtype.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) moe_gather_combine_kernel(const T* __restrict__ rows, const int64_t* __restrict__ row_of,
                                                                  const float* __restrict__ w, float* __restrict__ out,
-                                                                 int k, int H) {
-  const int64_t t = blockIdx.x;
-  for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < k; ++j)
-      acc = fmaf(w[t * k + j], to_f32<T>(rows[row_of[t * k + j] * H + c]), acc);
-    out[t * H + c] = acc;
+                                                                 int64_t tokens, int k, int H) {
+  struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
+  const int per = H / VEC;
+  const int64_t total = tokens * per;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / per;
+    const int c = (int)(idx - t * per) * VEC;
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const float wj = w[t * k + j];
+      const Pack r = *reinterpret_cast<const Pack*>(rows + row_of[t * k + j] * H + c);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(wj, to_f32<T>(r.v[e]), acc[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) out[t * H + c + e] = acc[e];
   }
 }
 
@@ -601,7 +612,12 @@ int cb_moe_gather_combine(const void* rows, const int64_t* row_of, const float* 
                           int dtype, cudaStream_t st) {
   if (tokens == 0) return 0;
   CB_DISPATCH_FLOAT(dtype, T, {
-    moe_gather_combine_kernel<T><<<(unsigned)tokens, 256, 0, st>>>((const T*)rows, row_of, w, out, k, H);
+    constexpr int V = 16 / sizeof(T);
+    const bool vec = H % V == 0 && ((uintptr_t)rows & 15) == 0;
+    const int64_t total = (int64_t)tokens * (vec ? H / V : H);
+    const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+    if (vec) moe_gather_combine_kernel<T, V><<<grid, 256, 0, st>>>((const T*)rows, row_of, w, out, tokens, k, H);
+    else moe_gather_combine_kernel<T, 1><<<grid, 256, 0, st>>>((const T*)rows, row_of, w, out, tokens, k, H);
   });
   return CB_LAUNCH_CHECK();
 }

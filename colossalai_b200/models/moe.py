@@ -215,7 +215,11 @@ class ClampedExpertFF(nn.Module):
     def route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         from ..ops.moe import router_topk
 
-        logits = F.linear(x.float(), self.router.weight.float())
+        if x.is_cuda and x.dtype != torch.float32 and self.router.weight.dtype == x.dtype:
+            # 16-bit operands are exact in fp32: products and sums of the router run in fp32 (fp32 accumulator kept)
+            logits = torch.mm(x, self.router.weight.t(), out_dtype=torch.float32)
+        else:
+            logits = F.linear(x.float(), self.router.weight.float())
         if x.dtype == torch.float32:            # 32-bit serving: IEEE exponentials
             p = torch.softmax(logits, -1)
             w, idx = torch.topk(p, self.spec.top, dim=-1)

@@ -418,8 +418,6 @@ def stream_add_norm(x: torch.Tensor, addends: Sequence[torch.Tensor] = (), row: 
         if row is not None:
             row = row.float().contiguous()
         ad = list(addends) + [None] * (4 - len(addends))
-        if weight is not None and k:
-            assert weight.dtype in (out_dtype, torch.float32)
         loader.check(_get_lib().cb_stream_add_norm(
             loader.ptr(x), loader.ptr(ad[0]), _i64(0 if ad[0] is None else ad[0].stride(0)),
             code(ad[0].dtype) if ad[0] is not None else 0, loader.ptr(ad[1]), _i64(0 if ad[1] is None else ad[1].stride(0)),

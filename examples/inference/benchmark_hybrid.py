@@ -294,6 +294,11 @@ def kernels_palilix(width: int, batch: int, in_len: int, kv_rank: int = 192, rot
         qs, qa = x(H * d), torch.empty(T, H * Dk, device=dev, dtype=dt)
         ms = _time(lambda: M.rotary_half(qs, qa, H, d, d - rot, Dk, kv_rank, rot, rot, tab_r, meta.token_pos), flush)
         rec("rotary_half(q part)", phase, ms, 2 * T * H * rot * 2, 0, like="rope_qkv")
+        qkv = x(H * d)                                      # Llama's in-place rotation of the same number of channels
+        cos, sin = ops.build_rope_cache(L, rot, 5e5, device=dev)
+        posl = meta.token_pos.long()
+        ms = _time(lambda: ops.rope_qkv(qkv, posl, cos, sin, H, 0, d, rot_dim=rot), flush)
+        rec("llama:rope_qkv", phase, ms, 2 * T * H * rot * 2, 0)
         qa.normal_()
         ms = _time(lambda: M.paged_bias_attention(qa, cache, cache, tables, meta, d ** -0.5, vdim=kv_rank), flush)
         kv_bytes = batch * L * Dk * 2
