@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(ScanParams p, ScanWor
 }
 
 template <int DK, int MODE>
-__global__ void __launch_bounds__(128, 4) state_scan_kernel(ScanParams p, ScanWork w) {
+__global__ void __launch_bounds__(128, DK > 128 ? 2 : 4) state_scan_kernel(ScanParams p, ScanWork w) {
   constexpr int RP = DK / SCAN_PARTS;  // rows per lane
   constexpr int RPP = RP + 4;          // a lane's rows start 4 floats further: the four 16-byte reads of a warp hit
   constexpr int DKP = SCAN_PARTS * RPP;  // different banks
@@ -425,12 +425,12 @@ template <int DK, int MODE> int launch_scan_dk(const ScanParams& p, const ScanWo
 }
 
 // workspace floats for `tokens` tokens: q, k rows, decay rows and write strengths (delta rule), value rows
-static inline int scan_dk(int dim) { return dim <= 16 ? 16 : dim <= 32 ? 32 : dim <= 64 ? 64 : 128; }
+static inline int scan_dk(int dim) { return dim <= 16 ? 16 : dim <= 32 ? 32 : dim <= 64 ? 64 : dim <= 128 ? 128 : 256; }
 static inline int scan_vp(int vdim) { return (vdim + SCAN_COLS - 1) / SCAN_COLS * SCAN_COLS; }
 
 template <int MODE, typename T>
 int launch_scan(const ScanParams& p, float* work, int64_t tokens, int nseq, cudaStream_t st) {
-  if (p.dim > 128) return (int)cudaErrorInvalidValue;
+  if (p.dim > 256) return (int)cudaErrorInvalidValue;
   ScanWork w;
   w.DK = scan_dk(p.dim);
   w.VP = scan_vp(p.vdim);
@@ -443,7 +443,8 @@ int launch_scan(const ScanParams& p, float* work, int64_t tokens, int nseq, cuda
   if (w.DK == 16) return launch_scan_dk<16, MODE>(p, w, nseq, st);
   if (w.DK == 32) return launch_scan_dk<32, MODE>(p, w, nseq, st);
   if (w.DK == 64) return launch_scan_dk<64, MODE>(p, w, nseq, st);
-  return launch_scan_dk<128, MODE>(p, w, nseq, st);
+  if (w.DK == 128) return launch_scan_dk<128, MODE>(p, w, nseq, st);
+  return launch_scan_dk<256, MODE>(p, w, nseq, st);
 }
 
 // ------------------------------------------------------------------------------------------------ norms
@@ -730,14 +731,18 @@ __global__ void __launch_bounds__(256) rotary_half_kernel(const T* __restrict__ 
 
 // One warp per token: the first `rank` columns of z are RMS-normalised with weight w (the latent), the last `rot` are
 // turned by the token's position; both go into the token's row of the paged cache [blocks, block_size, 1, rank + rot].
-template <typename T, typename TW>
-__global__ void __launch_bounds__(128) latent_kv_write_kernel(const T* __restrict__ z, int64_t ldz, const TW* __restrict__ w,
+// VEC = 8: a lane holds 8 adjacent latent columns per step in registers between the sum of squares and the store (16-byte
+// accesses; the launcher checks widths and alignment), else VEC = 1.
+template <typename T, typename TW, int VEC>
+__global__ void __launch_bounds__(256) latent_kv_write_kernel(const T* __restrict__ z, int64_t ldz, const TW* __restrict__ w,
                                                               float eps, int rank, int rot,
                                                               const float* __restrict__ table, T* __restrict__ cache,
                                                               const int* __restrict__ block_tables,
                                                               const int* __restrict__ token_seq,
                                                               const int* __restrict__ token_pos, int64_t tokens,
                                                               int block_size, int max_blocks) {
+  struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
+  constexpr int KEEP = 4;                              // register steps: rank up to 32 * VEC * KEEP stays in registers
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= tokens) return;
@@ -745,11 +750,36 @@ __global__ void __launch_bounds__(128) latent_kv_write_kernel(const T* __restric
   const int64_t row = (int64_t)block_tables[(int64_t)seq * max_blocks + pos / block_size] * block_size + pos % block_size;
   const T* zr = z + t * ldz;
   T* out = cache + row * (rank + rot);
+  Pack keep[KEEP];
   float ss = 0.f;
-  for (int i = lane; i < rank; i += 32) { const float v = to_f32<T>(zr[i]); ss = fmaf(v, v, ss); }
+#pragma unroll
+  for (int n = 0; n < KEEP; ++n) {
+    const int i = (lane + 32 * n) * VEC;
+    if (i < rank) {
+      keep[n] = *reinterpret_cast<const Pack*>(zr + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) { const float v = to_f32<T>(keep[n].v[e]); ss = fmaf(v, v, ss); }
+    }
+  }
+  for (int i = (lane + 32 * KEEP) * VEC; i < rank; i += 32 * VEC) {
+    const Pack a = *reinterpret_cast<const Pack*>(zr + i);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) { const float v = to_f32<T>(a.v[e]); ss = fmaf(v, v, ss); }
+  }
   ss = warp_sum(ss);
   const float r = 1.f / sqrtf(ss / (float)rank + eps);
-  for (int i = lane; i < rank; i += 32) out[i] = from_f32<T>(to_f32<T>(zr[i]) * r * to_f32<TW>(w[i]));
+  auto emit = [&](int i, const Pack& a) {
+    Pack o;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) o.v[e] = from_f32<T>(to_f32<T>(a.v[e]) * r * to_f32<TW>(w[i + e]));
+    *reinterpret_cast<Pack*>(out + i) = o;
+  };
+#pragma unroll
+  for (int n = 0; n < KEEP; ++n) {
+    const int i = (lane + 32 * n) * VEC;
+    if (i < rank) emit(i, keep[n]);
+  }
+  for (int i = (lane + 32 * KEEP) * VEC; i < rank; i += 32 * VEC) emit(i, *reinterpret_cast<const Pack*>(zr + i));
   const int half = rot >> 1;
   const float* cs = table + (int64_t)pos * rot;
   for (int i = lane; i < half; i += 32) {
@@ -1196,7 +1226,9 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
   }
 }
 
-// one warp per (token, head): joins the key chunks 0..pos / chunk in ascending order (log2-domain maxima)
+// one warp per (token, head, 32 value columns): joins the key chunks 0..pos / chunk (log2-domain maxima).  The chunks'
+// maxima and denominators are read with one chunk per lane and reduced over the warp; the weighted sum of the partial
+// outputs then walks the chunks in ascending order with the weights passed by shuffle, eight chunks' loads in flight.
 template <typename T>
 __global__ void __launch_bounds__(128) attention_merge_kernel(const float* __restrict__ part_o,
                                                               const float* __restrict__ part_ml,
@@ -1204,32 +1236,33 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const float* __res
                                                               int64_t tokens, int heads, int vdim, int chunk,
                                                               int max_splits, int sink) {
   const int lane = threadIdx.x & 31;
-  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (unit >= tokens * heads) return;
+  const int cblocks = (vdim + 31) >> 5;
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= tokens * heads * cblocks) return;
+  const int64_t unit = item / cblocks;
+  const int c = (int)(item % cblocks) * 32 + lane;
   const int nsp = token_pos[unit / heads] / chunk + 1;
+  const float* ml = part_ml + unit * max_splits * 2;
   float mm = sink ? 0.f : -INFINITY;
-  for (int sp = 0; sp < nsp; ++sp) mm = fmaxf(mm, part_ml[(unit * max_splits + sp) * 2]);
+  for (int sp = lane; sp < nsp; sp += 32) mm = fmaxf(mm, ml[sp * 2]);
+  mm = warp_max(mm);
   const float mu = mm == -INFINITY ? 0.f : mm;
-  float l = sink ? ex2f(0.f - mu) : 0.f;
-  float acc[ATT_MAX_VREG];
-#pragma unroll
-  for (int r = 0; r < ATT_MAX_VREG; ++r) acc[r] = 0.f;
-  for (int sp = 0; sp < nsp; ++sp) {
-    const float w = ex2f(part_ml[(unit * max_splits + sp) * 2] - mu);
-    l = fmaf(part_ml[(unit * max_splits + sp) * 2 + 1], w, l);
-    const float* po = part_o + (unit * max_splits + sp) * vdim;
-#pragma unroll
-    for (int r = 0; r < ATT_MAX_VREG; ++r) {
-      const int c = lane + 32 * r;
-      if (c < vdim) acc[r] = fmaf(po[c], w, acc[r]);
+  float l = 0.f;
+  for (int sp = lane; sp < nsp; sp += 32) l = fmaf(ml[sp * 2 + 1], ex2f(ml[sp * 2] - mu), l);
+  l = warp_sum(l) + (sink ? ex2f(0.f - mu) : 0.f);
+  float acc = 0.f;
+  const float* po = part_o + unit * max_splits * vdim;
+  for (int s0 = 0; s0 < nsp; s0 += 32) {
+    const float wl = s0 + lane < nsp ? ex2f(ml[(s0 + lane) * 2] - mu) : 0.f;      // weight of chunk s0 + lane
+    const int n = min(32, nsp - s0);
+#pragma unroll 8
+    for (int j = 0; j < n; ++j) {
+      const float w = __shfl_sync(0xffffffffu, wl, j);
+      if (c < vdim) acc = fmaf(po[(int64_t)(s0 + j) * vdim + c], w, acc);
     }
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
-#pragma unroll
-  for (int r = 0; r < ATT_MAX_VREG; ++r) {
-    const int c = lane + 32 * r;
-    if (c < vdim) out[unit * vdim + c] = from_f32<T>(acc[r] * inv);
-  }
+  if (c < vdim) out[unit * vdim + c] = from_f32<T>(acc * inv);
 }
 
 template <typename T, int D, int MT>
@@ -1256,7 +1289,7 @@ int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const 
                                 bias_table, lut, lut_n, nbuckets, (T*)out, heads, kv_heads, dim, vdim, ldv, block_size,
                                 max_blocks, scale, sink, chunk, max_splits, part_o, part_ml);
   if (chunk > 0) {
-    const int64_t units = tokens * heads;
+    const int64_t units = tokens * heads * ((vdim + 31) / 32);
     attention_merge_kernel<T><<<(unsigned)((units + 3) / 4), 128, 0, st>>>(part_o, part_ml, token_pos, (T*)out, tokens,
                                                                           heads, vdim, chunk, max_splits, sink);
   }
@@ -1435,18 +1468,24 @@ int cb_latent_kv_write(const void* z, int64_t ldz, const void* w, int w_dtype, f
                        int64_t tokens, int block_size, int max_blocks, int dtype, cudaStream_t st) {
   if (tokens == 0) return 0;
   if (rot & 1) return (int)cudaErrorInvalidValue;
-  const unsigned grid = (unsigned)((tokens + 3) / 4);
+  const unsigned grid = (unsigned)((tokens + 7) / 8);
+#define CB_LATENT_WRITE(T, TW, V)                                                                                     \
+  latent_kv_write_kernel<T, TW, V><<<grid, 256, 0, st>>>((const T*)z, ldz, (const TW*)w, eps, rank, rot, table,        \
+                                                         (T*)cache, block_tables, token_seq, token_pos, tokens,       \
+                                                         block_size, max_blocks)
   CB_DISPATCH_FLOAT(dtype, T, {
-    if (w_dtype == CB_F32)
-      latent_kv_write_kernel<T, float><<<grid, 128, 0, st>>>((const T*)z, ldz, (const float*)w, eps, rank, rot, table,
-                                                             (T*)cache, block_tables, token_seq, token_pos, tokens,
-                                                             block_size, max_blocks);
-    else if (w_dtype == dtype)
-      latent_kv_write_kernel<T, T><<<grid, 128, 0, st>>>((const T*)z, ldz, (const T*)w, eps, rank, rot, table, (T*)cache,
-                                                         block_tables, token_seq, token_pos, tokens, block_size, max_blocks);
-    else
+    constexpr int V = 16 / sizeof(T);
+    const bool vec = rank % V == 0 && (rank + rot) % V == 0 && ldz % V == 0 && ((uintptr_t)z & 15) == 0 &&
+                     ((uintptr_t)cache & 15) == 0;
+    if (w_dtype == CB_F32) {
+      if (vec) CB_LATENT_WRITE(T, float, V); else CB_LATENT_WRITE(T, float, 1);
+    } else if (w_dtype == dtype) {
+      if (vec) CB_LATENT_WRITE(T, T, V); else CB_LATENT_WRITE(T, T, 1);
+    } else {
       return (int)cudaErrorInvalidValue;
+    }
   });
+#undef CB_LATENT_WRITE
   return CB_LAUNCH_CHECK();
 }
 

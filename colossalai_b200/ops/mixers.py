@@ -265,8 +265,8 @@ def state_scan_decay(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, head_dec
     (`rotary_table`) the first `rot_dims` channels of every q / k head are turned by the token's position, in fp32, before
     `q_scale` / `k_scale` multiply them.  q, k [T, heads x dim], v [T, heads x vdim]; state [slots, heads, dim, vdim] fp32.
     Returns fp32 o."""
-    if dim > 128:
-        raise NotImplementedError("state_scan: key width above 128 is not supported")
+    if dim > 256:
+        raise NotImplementedError("state_scan: key width above 256 is not supported")
     if use_native(q):
         return _scan_native(0, q, k, v, None, None, head_decay, None, None, state, meta, heads, heads, dim, vdim,
                             act_silu, False, 0.0, q_scale, k_scale, rot_table, rot_dims)
@@ -303,8 +303,8 @@ def state_scan_delta(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_pr
     the head's matrix M [dim, vdim] is first decayed row by row (M <- diag(r) M), then corrected towards v along k
     (e = w * (v - M^T k); M <- M + outer(k, e)) and read after the write (y = M^T q).  q, k [T, qk_heads x dim] (head h reads
     h // (heads / qk_heads)), v [T, heads x vdim], decay_pre [T, heads x dim], beta_pre [T, heads]; fp32 state."""
-    if dim > 128:
-        raise NotImplementedError("state_scan: key width above 128 is not supported")
+    if dim > 256:
+        raise NotImplementedError("state_scan: key width above 256 is not supported")
     q_scale = dim ** -0.5 if q_scale is None else q_scale
     if use_native(q):
         return _scan_native(1, q, k, v, decay_pre, beta_pre, None, a_log, dt_bias, state, meta, heads, qk_heads, dim,

@@ -135,8 +135,17 @@ def serve(cfg: ModelConfig, batch: int, in_len: int, out_len: int, cuda_graph: b
     return out
 
 
-def _time(fn, flush, iters: int = 5) -> float:
+def _time(fn, flush, iters: int = 5, graph: bool = False) -> float:
+    """Median device time of `fn`.  `graph`: the launches are captured once and replayed, which takes the host's share
+    (python and launch latency, tens of microseconds) out of kernels that run for a few microseconds."""
     for _ in range(3):
+        fn()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g):
+            fn()
+        fn = g.replay
         fn()
     ts = []
     for _ in range(iters):
@@ -243,22 +252,23 @@ def kernels_palilix(width: int, batch: int, in_len: int, kv_rank: int = 192, rot
 
     def rec(name, phase, ms, bytes_, flops, like=""):
         ideal = max(bytes_ / hbm, flops / tflops) * 1e3
-        rows.append({"kernel": name, "phase": phase, "width": width, "ms": ms, "roofline_ms": ideal,
+        rows.append({"kernel": name, "phase": phase + ("(graph replay)" if phase == "decode" else ""), "width": width, "ms": ms, "roofline_ms": ideal,
                      "frac_of_" + src + "_roofline": ideal / ms, "bound": "hbm" if bytes_ / hbm > flops / tflops else "tensor",
                      "like": like})
 
     for phase, q_len, ctx in (("prefill", in_len, 0), ("decode", 1, in_len)):
+        replay = phase == "decode"             # decode kernels are timed as graph replays (no host share)
         T = batch * q_len
         meta = M.RaggedMeta.build([q_len] * batch, [ctx] * batch, list(range(batch)), dev)
         x = lambda c: torch.randn(T, c, device=dev, dtype=dt)
         # stream sum + layer norm  |  like: Gopunex norm + residual, Llama fused norm
         xs, y1, y2 = torch.randn(T, width, device=dev), x(width), x(width)
         w = torch.ones(width, device=dev, dtype=dt)
-        ms = _time(lambda: M.stream_add_norm(xs, [y1, y2], weight=w, eps=1e-5, kind="layer"), flush)
+        ms = _time(lambda: M.stream_add_norm(xs, [y1, y2], weight=w, eps=1e-5, kind="layer"), flush, graph=replay)
         rec("stream_add_norm(2 addends, layer norm)", phase, ms, T * width * (4 + 4 + 2 + 2 + 2), 0, like="rmsnorm_residual")
-        ms = _time(lambda: M.rms_norm_residual(xs, y1, w, 1e-5, 0.7, 1.0), flush)
+        ms = _time(lambda: M.rms_norm_residual(xs, y1, w, 1e-5, 0.7, 1.0), flush, graph=replay)
         rec("gopunex:rmsnorm_residual", phase, ms, T * width * (4 + 4 + 2 + 2), 0)
-        ms = _time(lambda: ops.rms_norm(y1, w, 1e-5, y2), flush)
+        ms = _time(lambda: ops.rms_norm(y1, w, 1e-5, y2), flush, graph=replay)
         rec("llama:rmsnorm_fwd(+residual)", phase, ms, T * width * 2 * 4, 0)
         # retention scan with rotary positions  |  like: the same scan without them (lightning attention)
         S = torch.zeros(batch, H, d, d, device=dev)
@@ -267,15 +277,15 @@ def kernels_palilix(width: int, batch: int, in_len: int, kv_rank: int = 192, rot
         dec = torch.full((H,), 0.97, device=dev)
         table = M.rotary_table(ctx + q_len, 64, 1e6, dev)
         ms = _time(lambda: M.state_scan_decay(q, k, v, dec, S, meta, H, d, d, act_silu=False, rot_table=table, rot_dims=64,
-                                              k_scale=d ** -0.5), flush)
+                                              k_scale=d ** -0.5), flush, graph=replay)
         rec("state_scan_decay+rotary", phase, ms, T * (3 * H * d * 2 + H * d * 4) + state_bytes, 4.0 * T * H * d * d,
             like="state_scan_decay")
-        ms = _time(lambda: M.state_scan_decay(q, k, v, dec, S, meta, H, d, d), flush)
+        ms = _time(lambda: M.state_scan_decay(q, k, v, dec, S, meta, H, d, d), flush, graph=replay)
         rec("gopunex:state_scan_decay", phase, ms, T * (3 * H * d * 2 + H * d * 4) + state_bytes, 4.0 * T * H * d * d)
         o, gate, wn = torch.randn(T, H * d, device=dev), x(H * d), torch.ones(d, device=dev, dtype=dt)
-        ms = _time(lambda: M.gated_group_rms_norm(o, None, gate, d, 1e-5, dt, gate_act="silu"), flush)
+        ms = _time(lambda: M.gated_group_rms_norm(o, None, gate, d, 1e-5, dt, gate_act="silu"), flush, graph=replay)
         rec("gated_group_rmsnorm(silu)", phase, ms, T * H * d * (4 + 2 + 2), 0, like="gated_group_rmsnorm")
-        ms = _time(lambda: M.gated_group_rms_norm(o, wn, gate, d, 1e-5, dt), flush)
+        ms = _time(lambda: M.gated_group_rms_norm(o, wn, gate, d, 1e-5, dt), flush, graph=replay)
         rec("gopunex:gated_group_rmsnorm", phase, ms, T * H * d * (4 + 2 + 2), 0)
         # latent attention: cache rows, query rotation, attention over the rows
         L = ctx + q_len
@@ -284,23 +294,23 @@ def kernels_palilix(width: int, batch: int, in_len: int, kv_rank: int = 192, rot
         tables = torch.arange(batch * per, dtype=torch.int32, device=dev).view(batch, per)
         z, nw = x(Dk), torch.ones(kv_rank, device=dev, dtype=dt)
         tab_r = M.rotary_table(L, rot, 5e5, dev)
-        ms = _time(lambda: M.latent_kv_write(z, nw, 1e-5, kv_rank, tab_r, cache, tables, meta), flush)
+        ms = _time(lambda: M.latent_kv_write(z, nw, 1e-5, kv_rank, tab_r, cache, tables, meta), flush, graph=replay)
         rec("latent_kv_write", phase, ms, 2 * T * Dk * 2, 0, like="paged_kv_write_mix")
         kc = torch.randn(batch * per, bs, G, d, device=dev, dtype=dt)
         vc = torch.randn(batch * per, bs, G, d, device=dev, dtype=dt)
         kk, vv = x(G * d), x(G * d)
-        ms = _time(lambda: M.paged_kv_write_mix(kk, vv, kc, vc, tables, meta), flush)
+        ms = _time(lambda: M.paged_kv_write_mix(kk, vv, kc, vc, tables, meta), flush, graph=replay)
         rec("gopunex:paged_kv_write_mix", phase, ms, 2 * T * 2 * G * d * 2, 0)
         qs, qa = x(H * d), torch.empty(T, H * Dk, device=dev, dtype=dt)
-        ms = _time(lambda: M.rotary_half(qs, qa, H, d, d - rot, Dk, kv_rank, rot, rot, tab_r, meta.token_pos), flush)
+        ms = _time(lambda: M.rotary_half(qs, qa, H, d, d - rot, Dk, kv_rank, rot, rot, tab_r, meta.token_pos), flush, graph=replay)
         rec("rotary_half(q part)", phase, ms, 2 * T * H * rot * 2, 0, like="rope_qkv")
         qkv = x(H * d)                                      # Llama's in-place rotation of the same number of channels
         cos, sin = ops.build_rope_cache(L, rot, 5e5, device=dev)
         posl = meta.token_pos.long()
-        ms = _time(lambda: ops.rope_qkv(qkv, posl, cos, sin, H, 0, d, rot_dim=rot), flush)
+        ms = _time(lambda: ops.rope_qkv(qkv, posl, cos, sin, H, 0, d, rot_dim=rot), flush, graph=replay)
         rec("llama:rope_qkv", phase, ms, 2 * T * H * rot * 2, 0)
         qa.normal_()
-        ms = _time(lambda: M.paged_bias_attention(qa, cache, cache, tables, meta, d ** -0.5, vdim=kv_rank), flush)
+        ms = _time(lambda: M.paged_bias_attention(qa, cache, cache, tables, meta, d ** -0.5, vdim=kv_rank), flush, graph=replay)
         kv_bytes = batch * L * Dk * 2
         att_flops = 2.0 * batch * H * (Dk + kv_rank) * (q_len * ctx + q_len * (q_len + 1) / 2)
         rec("latent_attention", phase, ms, kv_bytes + T * H * (Dk + kv_rank) * 2, att_flops,
@@ -310,25 +320,25 @@ def kernels_palilix(width: int, batch: int, in_len: int, kv_rank: int = 192, rot
         starts_host = M.log_bucket_starts(32, 512.0)
         starts = torch.tensor(starts_host, dtype=torch.int32, device=dev)
         lut = M.bucket_lut(starts_host).to(dev)
-        ms = _time(lambda: M.paged_bias_attention(qg, kc, vc, tables, meta, d ** -0.5, rel, starts, True, lut=lut), flush)
+        ms = _time(lambda: M.paged_bias_attention(qg, kc, vc, tables, meta, d ** -0.5, rel, starts, True, lut=lut), flush, graph=replay)
         g_bytes = 2 * batch * L * G * d * 2 + 2 * T * H * d * 2
         g_flops = 4.0 * batch * H * d * (q_len * ctx + q_len * (q_len + 1) / 2)
         rec("gopunex:paged_bias_attention", phase, ms, g_bytes, g_flops)
         if phase == "decode":
             lens = torch.full((batch,), L, dtype=torch.int32, device=dev)
-            ms = _time(lambda: iops.paged_decode_attention(qg.view(T, H, d), kc, vc, tables, lens, d ** -0.5), flush)
+            ms = _time(lambda: iops.paged_decode_attention(qg.view(T, H, d), kc, vc, tables, lens, d ** -0.5), flush, graph=replay)
             rec("llama:paged_decode_attention", phase, ms, g_bytes, g_flops)
         # experts: clamped gated unit (top 2 of every token), fp32 gather-combine
         I = width
         gu = x(2 * I).repeat(2, 1)
-        ms = _time(lambda: ops.clamped_glu(gu, 7.0, 1.702), flush)
+        ms = _time(lambda: ops.clamped_glu(gu, 7.0, 1.702), flush, graph=replay)
         rec("clamped_glu", phase, ms, 2 * T * 3 * I * 2, 0, like="glu_fwd(silu)")
-        ms = _time(lambda: ops.glu(gu, "silu"), flush)
+        ms = _time(lambda: ops.glu(gu, "silu"), flush, graph=replay)
         rec("llama:glu_fwd(silu)", phase, ms, 2 * T * 3 * I * 2, 0)
         ys = x(width).repeat(2, 1)
         row_of = torch.randperm(2 * T, device=dev).view(T, 2)
         wts = torch.rand(T, 2, device=dev)
-        ms = _time(lambda: gather_combine(ys, row_of, wts), flush)
+        ms = _time(lambda: gather_combine(ys, row_of, wts), flush, graph=replay)
         rec("moe_gather_combine", phase, ms, T * width * (2 * 2 + 4), 0)
     return rows
 

@@ -122,7 +122,7 @@ def _retention_oracle(q, k, v, decay, pos, dims, base):
 
 
 @pytest.mark.parametrize("tier", TIERS)
-@pytest.mark.parametrize("d,dv,dims", [(16, 24, 8), (32, 40, 32), (24, 8, 0)])
+@pytest.mark.parametrize("d,dv,dims", [(16, 24, 8), (32, 40, 32), (24, 8, 0), (160, 8, 64)])
 def test_retention_scan_carries_its_state_through_portions_and_slots(tier, d, dv, dims):
     """Two sequences in three steps: a whole prompt beside a portion, two-token portions, single tokens; the second
     sequence takes a slot that held another sequence before.  One head never forgets (decay 1)."""
@@ -183,11 +183,13 @@ def _latent_setup(dev, dtype, L, R, r, bs, seed):
 
 @pytest.mark.parametrize("tier", TIERS)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_latent_cache_rows_and_attention_in_the_latent_space(tier, dtype):
+@pytest.mark.parametrize("R,r", [(40, 8), (168, 24), (36, 6)])
+def test_latent_cache_rows_and_attention_in_the_latent_space(tier, dtype, R, r):
     """Rows [normalised latent | rotated key part] written in two portions; queries of the second portion and of a
-    decoded token attend over them; values are the rows' latent columns."""
+    decoded token attend over them; values are the rows' latent columns.  Row widths of 48 and 192 (two tile widths of
+    the tensor-core kernel in 16 bits) and 42 (no multiple of 8: the CUDA-core kernel)."""
     dev = _dev(tier)
-    L, R, r, bs, H = 300, 40, 8, 16, 4
+    L, bs, H = 300, 16, 4
     z, w, cache, tables, c, kr = _latent_setup(dev, dtype, L, R, r, bs, seed=20)
     table = M.rotary_table(L, r, 5e5, dev)
     first = 203                                                    # a cut inside a page
