@@ -972,7 +972,11 @@ CB_DEVICE void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
-template <typename T, int D, int MT>
+//
+// KS (decode steps: every sequence of the launch brings at most 16 rows = one m16 tile): the four warps share the SAME 16
+// rows and split each key tile between them (16 keys per warp) instead of three of them idling; every warp keeps its own
+// running maximum, denominator and accumulator, and the four are joined through shared memory at the end.
+template <typename T, int D, int MT, bool KS>
 __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bias_attention_mma_kernel(
     const T* __restrict__ q, int64_t ldq, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
@@ -983,6 +987,9 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
   constexpr int LDS = D + 8;                    // padded row: 16-byte aligned, conflict-free fragment reads
   constexpr int TILE = MMA_BN * LDS;
   constexpr int NR = 2 * MT;                    // rows a thread owns: (m-tile, upper / lower half)
+  constexpr int NT = KS ? 2 : MMA_BN / 8;       // n8 key tiles a warp scores per key tile
+  constexpr int KK = KS ? 1 : MMA_BN / 16;      // k16 steps of its P V product
+  static_assert(!KS || MT == 1, "the key-splitting form holds one m16 tile");
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // values that live in the key rows (latent attention: value = the row's first vdim columns): the K tile serves as V
@@ -1037,7 +1044,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
   bool valid[NR];
 #pragma unroll
   for (int e = 0; e < NR; ++e) {
-    rr[e] = row0 + warp * (16 * MT) + (e >> 1) * 16 + gid + 8 * (e & 1);
+    rr[e] = row0 + (KS ? 0 : warp * (16 * MT)) + (e >> 1) * 16 + gid + 8 * (e & 1);
     valid[e] = rr[e] < nrows;
     hr[e] = valid[e] ? rr[e] % R : 0;
     pos[e] = valid[e] ? ctx + rr[e] / R : -1;
@@ -1057,11 +1064,13 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
   }
   const float sc2 = scale * LOG2E;
   // first / last position any row of this warp sees: tiles beyond are skipped, tiles before need no causal test
-  const int wrow0 = row0 + warp * (16 * MT);
+  const int wrow0 = row0 + (KS ? 0 : warp * (16 * MT));
+  const int koff = KS ? warp * 16 : 0;          // first key of the warp inside a key tile
   const bool wlive = wrow0 < nrows;
   const int wlo = ctx + min(nrows - 1, wrow0) / R;
   const int whi = wlive ? ctx + min(nrows - 1, wrow0 + 16 * MT - 1) / R : -1;
-  const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + (warp * 16 * MT + (lane & 15)) * LDS + (lane >> 4) * 8);
+  const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + ((KS ? 0 : warp * 16 * MT) + (lane & 15)) * LDS +
+                                                             (lane >> 4) * 8);
 
   int stage = 0;
   for (int j0 = key_lo; j0 <= pos_max; j0 += MMA_BN, stage ^= 1) {
@@ -1072,17 +1081,17 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    if (j0 <= whi) {                            // warp-uniform: otherwise the whole tile is masked for this warp
+    if (j0 + koff <= whi) {                     // warp-uniform: otherwise the whole tile is masked for this warp
       const T* Ks = KV + stage * stage_elems;
       const T* Vs = kv_same ? Ks : Ks + TILE;
-      float sacc[MT][MMA_BN / 8][4];
+      float sacc[MT][NT][4];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < MMA_BN / 8; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
           for (int e = 0; e < 4; ++e) sacc[mt][nt][e] = 0.f;
-      const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(Ks + (lane & 7) * LDS + (lane >> 3) * 8);
+      const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(Ks + (koff + (lane & 7)) * LDS + (lane >> 3) * 8);
 #pragma unroll
       for (int kp = 0; kp < D / 32; ++kp) {     // two k-steps of 16 per pass
         uint32_t qa[MT][2][4];
@@ -1092,7 +1101,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
           ldsm_x4(qa[mt][1], q_addr + (mt * 16 * LDS + kp * 32 + 16) * (uint32_t)sizeof(T));
         }
 #pragma unroll
-        for (int nt = 0; nt < MMA_BN / 8; ++nt) {
+        for (int nt = 0; nt < NT; ++nt) {
           uint32_t kb[4];
           ldsm_x4(kb, k_addr + (nt * 8 * LDS + kp * 32) * (uint32_t)sizeof(T));
 #pragma unroll
@@ -1102,8 +1111,9 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
           }
         }
       }
-      const bool unmasked = j0 + MMA_BN - 1 <= wlo;
-      const bool far = nbuckets == 0 || wlo - (j0 + MMA_BN - 1) >= lut_n;     // every distance in the last bucket
+      const int jlast = j0 + koff + NT * 8 - 1;  // last key this warp scores in the tile
+      const bool unmasked = jlast <= wlo;
+      const bool far = nbuckets == 0 || wlo - jlast >= lut_n;                 // every distance in the last bucket
       float fb[NR];
 #pragma unroll
       for (int e = 0; e < NR; ++e) fb[e] = nbuckets > 0 ? tab[(nbuckets - 1) * R + hr[e]] : 0.f;
@@ -1114,7 +1124,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-          for (int nt = 0; nt < MMA_BN / 8; ++nt)
+          for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int r = mt * 2 + (e >> 1);
@@ -1126,10 +1136,10 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-          for (int nt = 0; nt < MMA_BN / 8; ++nt)
+          for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const int r = mt * 2 + (e >> 1), j = j0 + nt * 8 + tig * 2 + (e & 1);
+              const int r = mt * 2 + (e >> 1), j = j0 + koff + nt * 8 + tig * 2 + (e & 1);
               float sv = -INFINITY;
               if (j <= pos[r]) {
                 sv = sacc[mt][nt][e] * sc2;
@@ -1163,7 +1173,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < MMA_BN / 8; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int r = mt * 2 + (e >> 1);
@@ -1172,7 +1182,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
             l[r] += pe;
           }
 #pragma unroll
-      for (int kk = 0; kk < MMA_BN / 16; ++kk) {
+      for (int kk = 0; kk < KK; ++kk) {
         uint32_t pa[MT][4];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
@@ -1181,7 +1191,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
           pa[mt][2] = pack2<T>(sacc[mt][2 * kk + 1][0], sacc[mt][2 * kk + 1][1]);
           pa[mt][3] = pack2<T>(sacc[mt][2 * kk + 1][2], sacc[mt][2 * kk + 1][3]);
         }
-        const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(Vs + (kk * 16 + (lane & 15)) * LDS);
+        const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(Vs + (koff + kk * 16 + (lane & 15)) * LDS);
 #pragma unroll
         for (int nv = 0; nv < D / 8; ++nv) {
           uint32_t b0, b1;
@@ -1193,6 +1203,52 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
       }
     }
     __syncthreads();                            // this stage may be refilled in the next pass
+  }
+  if (KS) {
+    // the four warps' partial (maximum, denominator, accumulator) of the shared 16 rows meet in shared memory (the key
+    // loop's last barrier has released the K / V stages) and every thread joins a share of the (row, column) pairs
+    float* mg = reinterpret_cast<float*>(smem_raw);          // [4 warps][16 rows][D + 2]: columns, then m, l
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+      float* base = mg + (warp * 16 + gid + 8 * r) * (D + 2);
+#pragma unroll
+      for (int nv = 0; nv < D / 8; ++nv) {
+        base[nv * 8 + tig * 2] = o[0][nv][2 * r];
+        base[nv * 8 + tig * 2 + 1] = o[0][nv][2 * r + 1];
+      }
+      if (tig == 0) { base[D] = m[r]; base[D + 1] = l[r]; }
+    }
+    __syncthreads();
+    for (int e = tid; e < 16 * vdim; e += 128) {
+      const int rl = e / vdim, c = e - rl * vdim;
+      const int row = row0 + rl;
+      if (row >= nrows) break;
+      float mw[4], mall = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) { mw[w] = mg[(w * 16 + rl) * (D + 2) + D]; mall = fmaxf(mall, mw[w]); }
+      const float mu = mall == -INFINITY ? 0.f : mall;
+      float lsum = 0.f, osum = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = ex2f(mw[w] - mu);                     // m = -inf (no key seen) -> 0
+        lsum = fmaf(mg[(w * 16 + rl) * (D + 2) + D + 1], f, lsum);
+        osum = fmaf(mg[(w * 16 + rl) * (D + 2) + c], f, osum);
+      }
+      const int64_t unit = (int64_t)(t0 + row / R) * heads + g * R + row % R;
+      if (chunk > 0) {
+        part_o[(unit * max_splits + split) * vdim + c] = osum;
+        if (c == 0) {
+          part_ml[(unit * max_splits + split) * 2] = mall;
+          part_ml[(unit * max_splits + split) * 2 + 1] = lsum;
+        }
+      } else {
+        if (sink) lsum += ex2f(0.f - mu);
+        out[unit * vdim + c] = from_f32<T>(lsum > 0.f ? osum / lsum : 0.f);
+      }
+    }
+    return;
   }
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
@@ -1265,7 +1321,7 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const float* __res
   if (c < vdim) out[unit * vdim + c] = from_f32<T>(acc * inv);
 }
 
-template <typename T, int D, int MT>
+template <typename T, int D, int MT, bool KS = false>
 int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
                          const int* cu_q, const int* ctx_len, const int* token_pos, const float* bias_table,
                          const uint8_t* lut, int lut_n, int nbuckets, void* out, int64_t tokens, int nseq, int max_q,
@@ -1275,7 +1331,7 @@ int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const 
   constexpr int BM = 64 * MT;
   const bool kv_same = v_cache == k_cache && ldv == dim;
   const size_t smem = (size_t)((kv_same ? 2 : 4) * MMA_BN + BM) * (D + 8) * sizeof(T) + (size_t)nbuckets * R * sizeof(float);
-  auto kern = paged_bias_attention_mma_kernel<T, D, MT>;
+  auto kern = paged_bias_attention_mma_kernel<T, D, MT, KS>;
   static bool configured = false;               // per instantiation: opt in to large shared memory, all of it for CTAs
   if (!configured) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -1548,7 +1604,13 @@ int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache,
     return (int)cudaErrorInvalidValue;
   const int dmax = dim > vdim ? dim : vdim;
   const bool wide = max_q * (heads / kv_heads) > 64;      // 128 query rows per CTA (32 per warp) once a portion fills them
+  const bool few = max_q * (heads / kv_heads) <= 16;      // decode steps: one m16 tile per sequence, warps split the keys
 #define CB_ATT_MMA(T, D)                                                                                              \
+  if (few)                                                                                                            \
+    return launch_attention_mma<T, D, 1, true>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos,       \
+                                               bias_table, lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads,      \
+                                               kv_heads, dim, vdim, ldv, block_size, max_blocks, scale, sink, chunk,   \
+                                               max_splits, part_o, part_ml, st);                                       \
   if (wide)                                                                                                           \
     return launch_attention_mma<T, D, 2>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table, \
                                          lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,  \
@@ -1562,6 +1624,8 @@ int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache,
     else if (dmax <= 64) { CB_ATT_MMA(T, 64); }
     else if (dmax <= 128) { CB_ATT_MMA(T, 128); }
     else {                                               // 129..256 wide rows: one m16 tile per warp, one CTA per SM
+      // (no key-splitting form here: at this width joining four 16 x 256 accumulators through shared memory costs more
+      // than the three idle warps of a short decode CTA, measured 18.9 us against 14.1 us on 8 x 2048 keys)
       return launch_attention_mma<T, 256, 1>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table,
                                              lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,
                                              ldv, block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml,
