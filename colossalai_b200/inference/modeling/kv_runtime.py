@@ -154,7 +154,7 @@ class PagedKVRuntime:
             T, hq = q.shape[0], q.shape[1]
             o = self.attend_ragged(layer_idx, q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1), scale)
             return o.view(T, hq, -1)
-        kc, vc = self.k_caches[layer_idx], self.v_caches[layer_idx]
+        kc, vc = self.k_caches[self.cache_index(layer_idx)], self.v_caches[self.cache_index(layer_idx)]
         iops.kv_cache_write(k, v, kc, vc, self.block_tables, self.token_seq, self.token_pos)
         if sliding_window is not None and self.max_len_host > sliding_window:
             return self._attend_windowed(q, k, v, kc, vc, scale, alibi_slopes, sliding_window)

@@ -213,28 +213,35 @@ def test_latent_cache_rows_and_attention_in_the_latent_space(tier, dtype, R, r):
 
 @pytest.mark.parametrize("tier", TIERS)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("portion", [1, 23])
 @pytest.mark.parametrize("target", [0, 1, 15, 16, 17, 255, 256, 511])
-def test_one_far_key_singled_out_among_hundreds(tier, dtype, target):
-    """The query of the last token points at ONE key (the first tokens, both sides of a page border, far back): the
-    result must be that key's latent, whatever page it lies on."""
+def test_one_far_key_singled_out_among_hundreds(tier, dtype, target, portion):
+    """The query of the last token points at ONE key (the first tokens, both sides of a page border and of a key chunk's
+    edge, far back): the result must be that key's latent, whatever page it lies on - for a token decoded alone and for
+    the last token of a prompt's portion (the other rows of the portion carry small random queries)."""
     dev = _dev(tier)
     L, R, r, bs, H = 520, 32, 8, 16, 2
     z, w, cache, tables, c, kr = _latent_setup(dev, dtype, L, R, r, bs, seed=30 + target)
     table = M.rotary_table(L, r, 5e5, dev)
     M.latent_kv_write(z.to(dev), w.to(dev), 1e-5, R, table, cache, tables, M.RaggedMeta.build([L], [0], [0], dev))
     row = torch.cat([c, kr], -1)[target]
-    q = torch.stack([row * 6.0, -row * 6.0]).reshape(1, H * (R + r)).to(dtype)     # head 1 looks away from it
-    meta = M.RaggedMeta.build([1], [L - 1], [0], dev)
-    cache_q = cache.clone()
-    got = M.paged_bias_attention(q.to(dev), cache_q, cache_q, tables, meta, 1.0, vdim=R).view(H, R).double().cpu()
+    q = _rand(portion, H * (R + r), seed=50 + target, scale=0.3).to(F64)
+    q[-1] = torch.stack([row * 6.0, -row * 6.0]).reshape(H * (R + r))              # head 1 looks away from it
+    q = q.to(dtype)
+    meta = M.RaggedMeta.build([portion], [L - portion], [0], dev)
+    got = M.paged_bias_attention(q.to(dev), cache, cache, tables, meta, 1.0, vdim=R).view(portion, H, R).double().cpu()
     keys = torch.cat([c, kr], -1)
-    s = keys @ (row * 6.0)
-    p = torch.softmax(s, 0)
+    qd = q.to(F64).view(portion, H, R + r)
+    want = torch.zeros(portion, H, R, dtype=F64)
+    for i in range(portion):
+        n = L - portion + i + 1
+        for h in range(H):
+            want[i, h] = torch.softmax(keys[:n] @ qd[i, h], 0) @ c[:n]
+    p = torch.softmax(keys @ qd[-1, 0], 0)
     assert p[target] > 0.99                                         # the crafted key does stand out
-    want = torch.stack([p @ c, torch.softmax(-s, 0) @ c])
     tol = 1e-4 if dtype == torch.float32 else 3e-2
     assert (got - want).abs().max() < tol * c.abs().max()
-    assert (got[0] - c[target]).abs().max() < 0.05 * c.abs().max()
+    assert (got[-1, 0] - c[target]).abs().max() < 0.05 * c.abs().max()
 
 
 @pytest.mark.parametrize("tier", TIERS)
